@@ -226,6 +226,90 @@ AO_B200_API int ao_lm_ring_append(const void* kn, const void* vn, int64_t n, int
                                   const int32_t* slot, const int32_t* pos, const int32_t* ahead, void* ring_k, void* ring_v,
                                   void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Post-norm residual, full causal attention with a sink, matrix-state recurrences (decayed linear attention, state-space
+ * duality), sigmoid routers with group-limited choice, SiLU-gated experts.
+ */
+
+/* x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * post_w;  x[t] += add_rows[t];  x[t] += add_vec;
+ * h[t] = x[t] / sqrt(mean(x[t]^2) + eps) * next_w  (in `dt`).   Every part but x is optional (null): y with post_w (null:
+ * ones) is a sublayer's result entering through its own norm, add_rows (fp32 [n][width]) and add_vec (`dt` [width]) are
+ * what a pass over a looped span of layers adds in front of its first layer, next_w is the next sublayer's input norm. */
+AO_B200_API int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const void* post_w, const float* add_rows,
+                                        const void* add_vec, const void* next_w, int dt, float eps, int64_t n, int64_t width,
+                                        void* h, void* stream);
+
+/* ao_lm_qk_prep with what a design may put between the projection and the attention (each optional, null / 0 = none):
+ * biases added to the projection (`dt`; q_bias [H d], k_bias [G d], v_bias [G dv]), a weight per coordinate on the
+ * unit-RMS queries and keys (`dt` [d], shared by the heads), and a query temperature
+ * q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1). */
+AO_B200_API int ao_lm_qk_norm_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, const void* q_bias,
+                                   const void* k_bias, const void* v_bias, const void* q_weight, const void* k_weight,
+                                   float temp_coef, int temp_every, const int32_t* pos, int64_t n, int H, int G, int d, int dv,
+                                   float eps, int dt, float* qn, void* kn, void* vn, void* stream);
+
+/* ao_lm_chunk_attention / ao_lm_chunk_attention_prompt with gate and dist_bias optional (null) and a sink: exp(sink[head])
+ * (fp32 [H]; null: none) joins every row's softmax denominator, without a key or a value and unscaled.  With `chunk` = the
+ * rows of the ring (the longest sequence a slot holds) this is plain causal attention over a full key/value cache. */
+AO_B200_API int ao_lm_sink_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
+                                     int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
+                                     const float* sink, const int32_t* slot, const int32_t* pos, const int32_t* back,
+                                     const int32_t* tile_first, const int32_t* tile_count, int n_tiles, int H, int G, int d,
+                                     int dv, int chunk, float scale, float softcap, float out_scale, int n_split,
+                                     void* workspace, int64_t workspace_bytes, void* out, int64_t ld_out, void* stream);
+AO_B200_API int ao_lm_sink_attention_prompt(const float* qn, const void* kn, const void* vn, const void* ring_k,
+                                            const void* ring_v, int dt, const float* gate, int64_t ld_gate,
+                                            const float* dist_bias, int n_dist, const float* sink, const int32_t* slot,
+                                            const int32_t* pos, const int32_t* back, const int32_t* tile_first,
+                                            const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk,
+                                            float scale, float softcap, float out_scale, void* out, int64_t ld_out,
+                                            void* stream);
+
+/* Matrix-state recurrence per head: S_t = a_t S_(t-1) + b_t k_t v_t^T (S: d x dv, fp32 state[slots][H][d][dv], zeros at
+ * position 0), out[t][h] = S_t^T q_t + skip[h] v_t (fp32).  q and k rows hold G groups of d (head h reads group
+ * h / (H / G)), v rows H heads of dv; act = 1 applies SiLU to q, k and v on load.  a, b: fp32 [n][ld_ab] per (row, head);
+ * a == null: a_t = a_head[h] and b_t = 1 (a fixed decay per head).  seg_first / seg_count: the step's segments (runs of
+ * consecutive rows of one sequence), whole. */
+AO_B200_API int ao_lm_outer_recurrence(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                                       int act, const float* a, const float* b, int64_t ld_ab, const float* a_head,
+                                       const float* skip, int H, int G, int d, int dv, float* state, const int32_t* slot,
+                                       const int32_t* pos, const int32_t* seg_first, const int32_t* seg_count, int n_segments,
+                                       float* out, int64_t ld_out, void* stream);
+
+/* Input side of a state-space mixer, from an fp32 projection row: conv_out[t][c] = silu(conv_b[c] + sum_j conv_w[c][j] *
+ * u(t - (taps - 1 - j))) over the `channels` values at conv_off (inputs in front of the step from conv_state[slot][taps - 1]
+ * [channels], oldest first; zeros in front of position 0), and per head step = softplus(proj[t][dt_off + h] + dt_bias[h]),
+ * a_out = exp(-exp(a_log[h]) * step), b_out = step.  ao_lm_conv_state_save, after every reader has run, makes the last
+ * taps - 1 inputs of each segment (x = the projection at conv_off, row stride ldx) the slot's new memory. */
+AO_B200_API int ao_lm_ssd_prep(const float* proj, int64_t ld, int64_t conv_off, int64_t dt_off, int64_t n, int64_t channels,
+                               int taps, const void* conv_w, const void* conv_b, int dt, const float* conv_state,
+                               const int32_t* slot, const int32_t* pos, const int32_t* back, int H, const void* dt_bias,
+                               const void* a_log, float* conv_out, float* a_out, float* b_out, void* stream);
+AO_B200_API int ao_lm_conv_state_save(const float* x, int64_t ldx, int64_t n, int64_t channels, int taps, const int32_t* slot,
+                                      const int32_t* pos, const int32_t* back, const int32_t* ahead, float* state,
+                                      void* stream);
+
+/* RMS norm over each of `groups` equal parts of a row, with a gate:  mode 0: out = norm(y) * weight * sigmoid(gate);
+ * mode 1: out = norm(y * silu(gate)) * weight.  y, gate fp32 with row strides; out [n][width] in `dt`. */
+AO_B200_API int ao_lm_gated_group_norm(const float* y, int64_t ldy, const float* gate, int64_t ldg, int mode, int64_t n,
+                                       int64_t width, int groups, const void* weight, int dt, float eps, void* out,
+                                       void* stream);
+
+/* Router over fp32 logits[n][E]: s = sigmoid(logit), choice on s + correction (fp32 [E]; null: none), restricted to the
+ * `keep` best of n_groups equal groups of neighbouring experts (group score = sum of its two largest choice scores);
+ * idx[t][top] = the `top` largest choice scores (ties: lowest index), weight = s / (sum of the chosen s + 1e-20) * scale. */
+AO_B200_API int ao_lm_router_group_topk_logits(const float* logits, int64_t n, int E, int top, const float* correction,
+                                               int n_groups, int keep, float scale, int32_t* idx, float* weight,
+                                               void* stream);
+
+/* ao_lm_glu_act / ao_lm_expert_gate_up with the constant added to the up branch as a parameter:
+ * y = g * sigmoid(alpha * g) * (u + shift); limit = +inf, alpha = 1, shift = 0 is the plain SiLU-gated unit. */
+AO_B200_API int ao_lm_glu_act_shift(const void* gu, int dt, int64_t n, int64_t ff, float limit, float alpha, float shift, void* y,
+                                    void* stream);
+AO_B200_API int ao_lm_expert_gate_up_shift(const void* h, const void* w_gate, const void* w_up, int dt, const int32_t* idx,
+                                           int64_t n, int top, int64_t width, int64_t ff, int64_t expert_stride, float limit,
+                                           float alpha, float shift, void* y, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -172,6 +172,22 @@ LM_SIGNATURES = {
     "ao_lm_chunk_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
     "ao_lm_ring_append": [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ao_lm_postnorm_residual": [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _vp, _vp],
+    "ao_lm_qk_norm_prep": [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _f32,
+                           _i32, _vp, _vp, _vp, _vp],
+    "ao_lm_sink_attention": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                             _i32, _i32, _i32, _f32, _f32, _f32, _i32, _vp, _i64, _vp, _i64, _vp],
+    "ao_lm_sink_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+                                    _i32, _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
+    "ao_lm_outer_recurrence": [_vp, _i64, _vp, _i64, _vp, _i64, _i32, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp,
+                               _vp, _vp, _vp, _i32, _vp, _i64, _vp],
+    "ao_lm_ssd_prep": [_vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp,
+                       _vp],
+    "ao_lm_conv_state_save": [_vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ao_lm_gated_group_norm": [_vp, _i64, _vp, _i64, _i32, _i64, _i64, _i32, _vp, _i32, _f32, _vp, _vp],
+    "ao_lm_router_group_topk_logits": [_vp, _i64, _i32, _i32, _vp, _i32, _i32, _f32, _vp, _vp, _vp],
+    "ao_lm_glu_act_shift": [_vp, _i32, _i64, _i64, _f32, _f32, _f32, _vp, _vp],
+    "ao_lm_expert_gate_up_shift": [_vp, _vp, _vp, _i32, _vp, _i64, _i32, _i64, _i64, _i64, _f32, _f32, _f32, _vp, _vp],
 }
 _LM_RESTYPES = {"ao_lm_last_cuda_error": ctypes.c_char_p, "ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64,
                 "ao_lm_chunk_attention_workspace_bytes": _i64}

@@ -1,7 +1,7 @@
 """Per-sequence memory of the models: key/value caches of the gpt-fast Llama (plain and int8), and the state of
 sequence models that keep something else per request — compressed (latent) keys, the previous token's input of a
 token-shift layer, a ring of keys and values for attention that never looks past a fixed span, the state of a
-recurrence, the last inputs of a short convolution — in numbered slots that a host-side allocator hands out and takes
+recurrence (a vector or a matrix per head), the last inputs of a short convolution — in numbered slots that a host-side allocator hands out and takes
 back.
 """
 from typing import Dict, List, Optional
@@ -150,6 +150,19 @@ class RecurrentState(nn.Module):
     def __init__(self, n_slots, width, device=None):
         super().__init__()
         self.register_buffer("s", torch.zeros(n_slots, width, dtype=torch.float32, device=device))
+
+    def grow(self, n_slots):
+        self.s = _grown(self.s, n_slots)
+
+
+class MatrixState(nn.Module):
+    """The state of a recurrence that keeps a matrix per head (decayed linear attention, state-space duality): fp32
+    [slots][heads][rows][cols]; a sequence starts from zeros (the kernel does not read the slot at position 0, so a reused
+    slot needs no clearing)."""
+
+    def __init__(self, n_slots, heads, rows, cols, device=None):
+        super().__init__()
+        self.register_buffer("s", torch.zeros(n_slots, heads, rows, cols, dtype=torch.float32, device=device))
 
     def grow(self, n_slots):
         self.s = _grown(self.s, n_slots)

@@ -1,0 +1,76 @@
+"""Mixtures of gated-linear-unit experts on chosen (token, expert) pairs, for any family whose experts are
+y = W_down (g * sigmoid(alpha * g) * (u + shift)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit):
+a handful of tokens run as index-driven matrix-vector kernels (no host round trip: the step can be captured into a CUDA
+graph), many tokens are sorted by expert around grouped library GEMMs.  The router that makes idx / weight is the
+family's own."""
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def glu_unit(L, dt, x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, limit, alpha, shift, st, f32_out=True):
+    """One dense unit over all rows: GEMM [gate | up] -> activation kernel -> GEMM down.  -> ([n][W], launches)."""
+    n, ff = x.shape[0], w_down.shape[1]
+    gu = torch.mm(x, w_gu.t())
+    ya = torch.empty(n, ff, dtype=x.dtype, device=x.device)
+    _lib.lm_check(L.ao_lm_glu_act_shift(_p(gu), dt, n, ff, limit, alpha, shift, _p(ya), st), "glu_act")
+    if f32_out and x.dtype == torch.bfloat16:
+        return torch.mm(ya, w_down.t(), out_dtype=torch.float32), 3
+    return torch.mm(ya, w_down.t()), 3
+
+
+def chosen_experts(L, dt, xc: torch.Tensor, ridx: torch.Tensor, rwt: torch.Tensor, wgu: torch.Tensor, wd: torch.Tensor,
+                   out: torch.Tensor, limit: float, alpha: float, shift: float, gemv: bool, accumulate: bool, st) -> int:
+    """out (fp32 [n][W]) = (accumulate ? out : 0) + sum_k rwt[t][k] * expert ridx[t][k] of xc[t].
+    wgu [E][2 ff][W] (gate rows, then up rows), wd [E][W][ff].  Returns the launches made."""
+    n, W = xc.shape
+    E, top, ff = wgu.shape[0], ridx.shape[1], wd.shape[2]
+    tdt, dev = xc.dtype, xc.device
+    esz = wgu.element_size()
+    if gemv:
+        ya = torch.empty(n * top, ff, dtype=tdt, device=dev)
+        _lib.lm_check(L.ao_lm_expert_gate_up_shift(_p(xc), _p(wgu), _p(wgu) + ff * W * esz, dt, _p(ridx), n, top, W, ff, 2 * ff * W,
+                                                   limit, alpha, shift, _p(ya), st), "expert_gate_up")
+        _lib.lm_check(L.ao_lm_expert_down(_p(ya), _p(wd), dt, _p(ridx), _p(rwt), n, top, W, ff, 1 if accumulate else 0, _p(out), st),
+                      "expert_down")
+        return 2
+    launches = 0
+    if not accumulate:
+        out.zero_()
+        launches += 1
+    # rows sorted by expert: one grouped GEMM per projection (bf16), or one exact GEMM pair per expert that has rows (fp32)
+    flat = ridx.view(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=E)
+    mrows = n * top
+    grouped = tdt == torch.bfloat16 and W % 8 == 0 and ff % 8 == 0 and hasattr(torch, "_grouped_mm")
+    xs = torch.empty(mrows, W, dtype=tdt, device=dev)
+    _lib.lm_check(L.ao_lm_gather_rows(_p(xc), dt, _p(order), top, mrows, W, _p(xs), st), "gather_rows")
+    if grouped:
+        offs = torch.cumsum(counts, 0).to(torch.int32)
+        gu = torch._grouped_mm(xs, wgu.transpose(1, 2), offs=offs)
+        ya = torch.empty(mrows, ff, dtype=tdt, device=dev)
+        _lib.lm_check(L.ao_lm_glu_act_shift(_p(gu), dt, mrows, ff, limit, alpha, shift, _p(ya), st), "glu_act")
+        ys = torch._grouped_mm(ya, wd.transpose(1, 2), offs=offs)
+        _lib.lm_check(L.ao_lm_scatter_add_rows(_p(ys), dt, _p(order), _p(rwt), top, mrows, W, _p(out), st), "scatter_add_rows")
+        return launches + 9
+    counts = counts.tolist()
+    ys = torch.empty(mrows, W, dtype=tdt, device=dev)
+    ya = torch.empty(max(counts), ff, dtype=tdt, device=dev)
+    at = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        gu = torch.mm(xs[at:at + c], wgu[e].t())
+        _lib.lm_check(L.ao_lm_glu_act_shift(_p(gu), dt, c, ff, limit, alpha, shift, _p(ya), st), "glu_act")
+        torch.mm(ya[:c], wd[e].t(), out=ys[at:at + c])
+        at += c
+        launches += 3
+    _lib.lm_check(L.ao_lm_scatter_add_rows(_p(ys), dt, _p(order), _p(rwt), top, mrows, W, _p(out), st), "scatter_add_rows")
+    return launches + 4

@@ -42,6 +42,9 @@ def _load_builtin():
     from .tadolix import model as _tadolix
     register(Family("tadolix", from_folder=_tadolix.Tadolix.from_checkpoint, from_name=_tadolix.Tadolix.from_name,
                     names=lambda: list(_tadolix.tadolix_configs)))
+    from .rutusun import model as _rutusun
+    register(Family("rutusun", from_folder=_rutusun.Rutusun.from_checkpoint, from_name=_rutusun.Rutusun.from_name,
+                    names=lambda: list(_rutusun.rutusun_configs)))
 
 
 def architecture_of(folder) -> str:

@@ -197,6 +197,9 @@ class _RunState:
     rec: Optional[RecurrentState] = None
     conv: Optional[ConvState] = None
 
+    def parts(self):
+        return [p for p in (self.canon, self.ring, self.rec, self.conv) if p is not None]
+
 
 class Tadolix(nn.Module):
     def __init__(self, config: TadolixArgs, weights: Dict[str, torch.Tensor], device="cuda", dtype=torch.bfloat16):

@@ -44,6 +44,44 @@ __global__ void qk_prep_kernel(const float* __restrict__ proj, int64_t ld, int64
   for (int c = threadIdx.x; c < G * dv; c += blockDim.x) stf(vn + t * G * dv + c, row[v_off + c]);
 }
 
+// The same split with what a design may put between the projection and the attention: biases added to the projection,
+// a learned weight per coordinate on the unit-RMS queries and keys (shared by all heads), and a query temperature that
+// grows with the position: q *= 1 + coef * ln(floor((pos + 1) / every) + 1).
+template <typename T>
+__global__ void qk_norm_prep_kernel(const float* __restrict__ proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off,
+                                    const T* __restrict__ q_bias, const T* __restrict__ k_bias, const T* __restrict__ v_bias,
+                                    const T* __restrict__ q_weight, const T* __restrict__ k_weight, float temp_coef,
+                                    int temp_every, const int32_t* __restrict__ pos, int H, int G, int d, int dv, float eps,
+                                    float* __restrict__ qn, T* __restrict__ kn, T* __restrict__ vn) {
+  const int64_t t = blockIdx.x;
+  const float* row = proj + t * ld;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float temp = 1.f;
+  if (temp_coef != 0.f) temp = 1.f + temp_coef * logf((float)((pos[t] + 1) / temp_every) + 1.f);
+  for (int h = warp; h < H + G; h += nw) {
+    const bool is_q = h < H;
+    const int64_t off = is_q ? (int64_t)h * d : (int64_t)(h - H) * d;
+    const float* src = row + (is_q ? q_off : k_off) + off;
+    const T* bias = is_q ? q_bias : k_bias;
+    const T* wt = is_q ? q_weight : k_weight;
+    float ss = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      const float v = src[c] + (bias ? ldf(bias + off + c) : 0.f);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float k = (is_q ? temp : 1.f) / sqrtf(ss / (float)d + eps);
+    for (int c = lane; c < d; c += 32) {
+      const float v = (src[c] + (bias ? ldf(bias + off + c) : 0.f)) * k * (wt ? ldf(wt + c) : 1.f);
+      if (is_q)
+        qn[(t * H + h) * d + c] = v;
+      else
+        stf(kn + (t * G + (h - H)) * d + c, v);
+    }
+  }
+  for (int c = threadIdx.x; c < G * dv; c += blockDim.x) stf(vn + t * G * dv + c, row[v_off + c] + (v_bias ? ldf(v_bias + c) : 0.f));
+}
+
 template <typename T>
 __global__ void ring_append_kernel(const T* __restrict__ kn, const T* __restrict__ vn, int64_t krow, int64_t vrow, int C,
                                    const int32_t* __restrict__ slot, const int32_t* __restrict__ pos,
@@ -59,10 +97,11 @@ struct ChunkArgs {
   const float* qn;           // [n][H][d]
   const void *kn, *vn;       // step rows [n][G][d], [n][G][dv]
   const void *ring_k, *ring_v;
-  const float* gate;         // pre-activation, row stride ld_gate, H * dv per row
+  const float* gate;         // pre-activation, row stride ld_gate, H * dv per row; null: no gate
   int64_t ld_gate;
-  const float* bias;         // [H][n_dist]
+  const float* bias;         // [H][n_dist]; null: none
   int n_dist;
+  const float* sink;         // [H]: exp(sink) joins every row's denominator; null: none
   const int32_t *slot, *pos, *back, *tile_first, *tile_count;
   int H, G, d, dv, C;
   float scale, softcap, out_scale;
@@ -141,7 +180,7 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
       if (kk <= lim) {
         sc *= a.scale;
         if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
-        sc += a.bias[(int64_t)qh * a.n_dist + min(lim - kk, a.n_dist - 1)];
+        if (a.bias) sc += a.bias[(int64_t)qh * a.n_dist + min(lim - kk, a.n_dist - 1)];
       } else {
         sc = -INFINITY;
       }
@@ -187,13 +226,13 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
     if (pr >= npairs) continue;
     const int r = pr / rep, qh = g * rep + pr % rep;
     const int64_t t = first + r;
-    const float inv = a.out_scale / den[s];
-    const float* gt = a.gate + t * a.ld_gate + (int64_t)qh * dv;
+    const float inv = a.out_scale / (a.sink ? den[s] + expf(a.sink[qh] - mx[s]) : den[s]);
+    const float* gt = a.gate ? a.gate + t * a.ld_gate + (int64_t)qh * dv : nullptr;
     T* dst = static_cast<T*>(a.out) + t * a.ld_out + (int64_t)qh * dv;
 #pragma unroll
     for (int e = 0; e < kMaxDvLane; ++e) {
       const int c = lane + 32 * e;
-      if (c < dv) stf(dst + c, o[s][e] * inv / (1.f + expf(-gt[c])));
+      if (c < dv) stf(dst + c, gt ? o[s][e] * inv / (1.f + expf(-gt[c])) : o[s][e] * inv);
     }
   }
 }
@@ -219,7 +258,8 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_merge_kernel(Chun
     float fz[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) fz[i] = mz[i] == -INFINITY ? 0.f : expf(mz[i] - top);
-    const float den = warp_sum(dz[0] * fz[0] + dz[1] * fz[1]);
+    float den = warp_sum(dz[0] * fz[0] + dz[1] * fz[1]);
+    if (a.sink) den += expf(a.sink[g * rep + pr % rep] - top);
     float o[kMaxDvLane];
 #pragma unroll
     for (int e = 0; e < kMaxDvLane; ++e) o[e] = 0.f;
@@ -244,12 +284,12 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_merge_kernel(Chun
     const int r = pr / rep, qh = g * rep + pr % rep;
     const int64_t t = first + r;
     const float inv = a.out_scale / den;
-    const float* gt = a.gate + t * a.ld_gate + (int64_t)qh * dv;
+    const float* gt = a.gate ? a.gate + t * a.ld_gate + (int64_t)qh * dv : nullptr;
     T* dst = static_cast<T*>(a.out) + t * a.ld_out + (int64_t)qh * dv;
 #pragma unroll
     for (int e = 0; e < kMaxDvLane; ++e) {
       const int c = lane + 32 * e;
-      if (c < dv) stf(dst + c, o[e] * inv / (1.f + expf(-gt[c])));
+      if (c < dv) stf(dst + c, gt ? o[e] * inv / (1.f + expf(-gt[c])) : o[e] * inv);
     }
   }
 }
@@ -275,6 +315,18 @@ extern "C" int ao_lm_qk_prep(const float* proj, int64_t ld, int64_t q_off, int64
   return lm_launch_status();
 }
 
+extern "C" int ao_lm_qk_norm_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, const void* q_bias,
+                                  const void* k_bias, const void* v_bias, const void* q_weight, const void* k_weight,
+                                  float temp_coef, int temp_every, const int32_t* pos, int64_t n, int H, int G, int d, int dv,
+                                  float eps, int dt, float* qn, void* kn, void* vn, void* stream) {
+  LM_CHECK_ARG(proj && qn && kn && vn && n > 0 && H > 0 && G > 0 && d > 0 && dv > 0 && (temp_coef == 0.f || (pos && temp_every > 0)));
+  LM_DISPATCH(dt, qk_norm_prep_kernel<T><<<(unsigned)n, 128, 0, lm_stream(stream)>>>(
+                      proj, ld, q_off, k_off, v_off, static_cast<const T*>(q_bias), static_cast<const T*>(k_bias),
+                      static_cast<const T*>(v_bias), static_cast<const T*>(q_weight), static_cast<const T*>(k_weight), temp_coef,
+                      temp_every, pos, H, G, d, dv, eps, qn, static_cast<T*>(kn), static_cast<T*>(vn)));
+  return lm_launch_status();
+}
+
 extern "C" int ao_lm_ring_append(const void* kn, const void* vn, int64_t n, int64_t k_row, int64_t v_row, int ring, int dt,
                                  const int32_t* slot, const int32_t* pos, const int32_t* ahead, void* ring_k, void* ring_v,
                                  void* stream) {
@@ -296,14 +348,14 @@ extern "C" int64_t ao_lm_chunk_attention_workspace_bytes(int n_tiles, int G, int
   return n_split > 1 ? (int64_t)n_tiles * G * n_split * (kWarps * kPairSlots) * (dv + 2) * 4 : 0;
 }
 
-extern "C" int ao_lm_chunk_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
-                                     int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
-                                     const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
-                                     const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk, float scale,
-                                     float softcap, float out_scale, int n_split, void* workspace, int64_t workspace_bytes,
-                                     void* out, int64_t ld_out, void* stream) {
-  LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && gate && dist_bias && slot && pos && back && tile_first && tile_count && out);
-  LM_CHECK_ARG(n_tiles > 0 && n_dist > 0 && chunk > 0 && G > 0 && G <= 65535 && n_split >= 1 && n_split <= 64);
+extern "C" int ao_lm_sink_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
+                                    int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
+                                    const float* sink, const int32_t* slot, const int32_t* pos, const int32_t* back,
+                                    const int32_t* tile_first, const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv,
+                                    int chunk, float scale, float softcap, float out_scale, int n_split, void* workspace,
+                                    int64_t workspace_bytes, void* out, int64_t ld_out, void* stream) {
+  LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && slot && pos && back && tile_first && tile_count && out);
+  LM_CHECK_ARG(n_tiles > 0 && (!dist_bias || n_dist > 0) && chunk > 0 && G > 0 && G <= 65535 && n_split >= 1 && n_split <= 64);
   if (n_split > 1) {
     LM_CHECK_ARG(workspace);
     if (workspace_bytes < ao_lm_chunk_attention_workspace_bytes(n_tiles, G, dv, n_split)) return AO_B200_ERR_WORKSPACE;
@@ -311,7 +363,7 @@ extern "C" int ao_lm_chunk_attention(const float* qn, const void* kn, const void
   if (generic_tile_rows(H, G) == 0 || dv > 32 * kMaxDvLane) return AO_B200_ERR_UNSUPPORTED;
   const size_t smem = generic_smem(d, dv);
   if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
-  ChunkArgs a{qn, kn, vn, ring_k, ring_v, gate, ld_gate, dist_bias, n_dist, slot, pos, back, tile_first, tile_count,
+  ChunkArgs a{qn, kn, vn, ring_k, ring_v, gate, ld_gate, dist_bias, n_dist, sink, slot, pos, back, tile_first, tile_count,
               H, G, d, dv, chunk, scale, softcap, out_scale, out, ld_out, n_split, static_cast<float*>(workspace)};
   LM_DISPATCH(dt, {
     auto kern = chunk_attention_kernel<T>;
@@ -327,4 +379,16 @@ extern "C" int ao_lm_chunk_attention(const float* qn, const void* kn, const void
       chunk_attention_merge_kernel<T><<<dim3((unsigned)n_tiles, (unsigned)G), kWarps * 32, 0, lm_stream(stream)>>>(a);
   });
   return lm_launch_status();
+}
+
+extern "C" int ao_lm_chunk_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
+                                     int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
+                                     const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
+                                     const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk, float scale,
+                                     float softcap, float out_scale, int n_split, void* workspace, int64_t workspace_bytes,
+                                     void* out, int64_t ld_out, void* stream) {
+  LM_CHECK_ARG(gate && dist_bias);
+  return ao_lm_sink_attention(qn, kn, vn, ring_k, ring_v, dt, gate, ld_gate, dist_bias, n_dist, nullptr, slot, pos, back,
+                              tile_first, tile_count, n_tiles, H, G, d, dv, chunk, scale, softcap, out_scale, n_split, workspace,
+                              workspace_bytes, out, ld_out, stream);
 }

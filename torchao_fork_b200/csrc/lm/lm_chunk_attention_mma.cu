@@ -69,8 +69,9 @@ struct PromptArgs {
   const __nv_bfloat16 *ring_k, *ring_v;  // [slots][C][G][d], [slots][C][G][dv]
   const float* gate;
   int64_t ld_gate;
-  const float* bias;                     // [H][n_dist]
+  const float* bias;                     // [H][n_dist]; null: none
   int n_dist;
+  const float* sink;                     // [H]; null: none
   const int32_t *slot, *pos, *back, *tile_first, *tile_count;
   int H, G, d, C;
   float scale, softcap, out_scale;
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(kPWarps * 32) chunk_attention_prompt_kernel(Pr
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows 16 warp + g4 and + 8 (l: this thread's share)
   const int r0 = warp * 16 + g4, r1 = r0 + 8;
   const int lim0 = r0 < count ? off0 + r0 : -1, lim1 = r1 < count ? off0 + r1 : -1;   // the rows' own key indices
-  const float* bias = a.bias + (int64_t)h * a.n_dist;
+  const float* bias = a.bias ? a.bias + (int64_t)h * a.n_dist : nullptr;
   const int nd1 = a.n_dist - 1;
   // ldmatrix row addresses of this lane: A (queries), B (keys), B transposed (values)
   const T* qa_ptr = Qs + (size_t)(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QP + (lane >> 4) * 8;
@@ -183,12 +184,12 @@ __global__ void __launch_bounds__(kPWarps * 32) chunk_attention_prompt_kernel(Pr
         if (key <= lim0) {
           v0 = s[i][e] * a.scale;
           if (cap > 0.f) v0 = cap * tanh_fast(v0 * inv_cap);
-          v0 += __ldg(bias + min(lim0 - key, nd1));
+          if (bias) v0 += __ldg(bias + min(lim0 - key, nd1));
         }
         if (key <= lim1) {
           v1 = s[i][2 + e] * a.scale;
           if (cap > 0.f) v1 = cap * tanh_fast(v1 * inv_cap);
-          v1 += __ldg(bias + min(lim1 - key, nd1));
+          if (bias) v1 += __ldg(bias + min(lim1 - key, nd1));
         }
         s[i][e] = v0, s[i][2 + e] = v1;
         mx0 = fmaxf(mx0, v0);
@@ -267,6 +268,11 @@ __global__ void __launch_bounds__(kPWarps * 32) chunk_attention_prompt_kernel(Pr
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (a.sink) {   // the sink joins the denominator once, on the scale of the row's running maximum
+    const float sk = a.sink[h];
+    l0 += expf(sk - m0);
+    l1 += expf(sk - m1);
+  }
   const bool pair_store = a.ld_out % 2 == 0;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -274,11 +280,11 @@ __global__ void __launch_bounds__(kPWarps * 32) chunk_attention_prompt_kernel(Pr
     if (r >= count) continue;
     const int64_t t = first + r;
     const float k = a.out_scale / (half ? l1 : l0);
-    const float* gt = a.gate + t * a.ld_gate + (int64_t)h * DV + 2 * t4;
+    const float* gt = a.gate ? a.gate + t * a.ld_gate + (int64_t)h * DV + 2 * t4 : nullptr;
     T* dst = a.out + t * a.ld_out + (int64_t)h * DV + 2 * t4;
 #pragma unroll
     for (int i = 0; i < 2 * NV; ++i) {
-      const float g0 = 1.f / (1.f + expf(-gt[i * 8])), g1 = 1.f / (1.f + expf(-gt[i * 8 + 1]));
+      const float g0 = gt ? 1.f / (1.f + expf(-gt[i * 8])) : 1.f, g1 = gt ? 1.f / (1.f + expf(-gt[i * 8 + 1])) : 1.f;
       const float y0 = o[i][2 * half] * k * g0, y1 = o[i][2 * half + 1] * k * g1;
       if (pair_store) {
         *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(y0, y1);
@@ -322,14 +328,15 @@ extern "C" int ao_lm_chunk_attention_prompt_plan(int dt, int H, int G, int d, in
   return AO_B200_OK;
 }
 
-extern "C" int ao_lm_chunk_attention_prompt(const float* qn, const void* kn, const void* vn, const void* ring_k,
-                                            const void* ring_v, int dt, const float* gate, int64_t ld_gate,
-                                            const float* dist_bias, int n_dist, const int32_t* slot, const int32_t* pos,
-                                            const int32_t* back, const int32_t* tile_first, const int32_t* tile_count,
-                                            int n_tiles, int H, int G, int d, int dv, int chunk, float scale, float softcap,
-                                            float out_scale, void* out, int64_t ld_out, void* stream) {
-  LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && gate && dist_bias && slot && pos && back && tile_first && tile_count && out);
-  LM_CHECK_ARG(n_tiles > 0 && n_dist > 0 && chunk > 0 && H > 0 && H <= 65535);
+extern "C" int ao_lm_sink_attention_prompt(const float* qn, const void* kn, const void* vn, const void* ring_k,
+                                           const void* ring_v, int dt, const float* gate, int64_t ld_gate,
+                                           const float* dist_bias, int n_dist, const float* sink, const int32_t* slot,
+                                           const int32_t* pos, const int32_t* back, const int32_t* tile_first,
+                                           const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk,
+                                           float scale, float softcap, float out_scale, void* out, int64_t ld_out,
+                                           void* stream) {
+  LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && slot && pos && back && tile_first && tile_count && out);
+  LM_CHECK_ARG(n_tiles > 0 && (!dist_bias || n_dist > 0) && chunk > 0 && H > 0 && H <= 65535);
   if (!prompt_ok(dt, H, G, d, dv)) return AO_B200_ERR_UNSUPPORTED;
   // 16-byte copies of queries, keys and values; the result is stored in pairs when its rows allow it
   LM_CHECK_ARG(reinterpret_cast<uintptr_t>(out) % 4 == 0 && reinterpret_cast<uintptr_t>(qn) % 16 == 0 &&
@@ -337,7 +344,7 @@ extern "C" int ao_lm_chunk_attention_prompt(const float* qn, const void* kn, con
                reinterpret_cast<uintptr_t>(ring_k) % 16 == 0 && reinterpret_cast<uintptr_t>(ring_v) % 16 == 0);
   using T = __nv_bfloat16;
   PromptArgs a{qn, static_cast<const T*>(kn), static_cast<const T*>(vn), static_cast<const T*>(ring_k),
-               static_cast<const T*>(ring_v), gate, ld_gate, dist_bias, n_dist, slot, pos, back, tile_first, tile_count,
+               static_cast<const T*>(ring_v), gate, ld_gate, dist_bias, n_dist, sink, slot, pos, back, tile_first, tile_count,
                H, G, d, chunk, scale, softcap, out_scale, static_cast<T*>(out), ld_out};
   const cudaStream_t st = lm_stream(stream);
 #define LM_CP(NV) \
@@ -346,4 +353,16 @@ extern "C" int ao_lm_chunk_attention_prompt(const float* qn, const void* kn, con
   switch (dv / 16) { LM_CP(1) LM_CP(2) LM_CP(3) LM_CP(4) LM_CP(5) LM_CP(6) LM_CP(7) LM_CP(8) }
 #undef LM_CP
   return AO_B200_ERR_UNSUPPORTED;
+}
+
+extern "C" int ao_lm_chunk_attention_prompt(const float* qn, const void* kn, const void* vn, const void* ring_k,
+                                            const void* ring_v, int dt, const float* gate, int64_t ld_gate,
+                                            const float* dist_bias, int n_dist, const int32_t* slot, const int32_t* pos,
+                                            const int32_t* back, const int32_t* tile_first, const int32_t* tile_count,
+                                            int n_tiles, int H, int G, int d, int dv, int chunk, float scale, float softcap,
+                                            float out_scale, void* out, int64_t ld_out, void* stream) {
+  LM_CHECK_ARG(gate && dist_bias);
+  return ao_lm_sink_attention_prompt(qn, kn, vn, ring_k, ring_v, dt, gate, ld_gate, dist_bias, n_dist, nullptr, slot, pos, back,
+                                     tile_first, tile_count, n_tiles, H, G, d, dv, chunk, scale, softcap, out_scale, out, ld_out,
+                                     stream);
 }

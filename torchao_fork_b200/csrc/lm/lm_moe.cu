@@ -95,11 +95,93 @@ __global__ void router_topk_logits_kernel(const float* __restrict__ logits, int6
   softmax_topk(z, E, top, lane, idx + t * top, weight + t * top);
 }
 
+// Sigmoid router with a selection correction and group-limited choice, one warp per token over fp32 logits:
+//   s_e = sigmoid(z_e); the choice is made on c_e = s_e + correction_e.  The experts form n_groups equal groups of
+//   neighbours; a group's score is the sum of its two largest c (of its only one, for groups of one); only experts of
+//   the `keep` best groups can be chosen (the others count as -inf); the `top` largest c win (ties: lowest index);
+//   weight = s_e / (sum of the chosen s + 1e-20) * scale.
+// Shared memory per warp: s [E], c [E], group scores [n_groups].
+__global__ void router_group_topk_kernel(const float* __restrict__ logits, int64_t n, int E, int top,
+                                         const float* __restrict__ correction, int n_groups, int keep, float scale,
+                                         int32_t* __restrict__ idx, float* __restrict__ weight) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * kWarps + warp;
+  if (t >= n) return;
+  float* s = sm + (size_t)warp * (2 * E + n_groups);
+  float* c = s + E;
+  float* gs = c + E;
+  for (int e = lane; e < E; e += 32) {
+    const float v = 1.f / (1.f + expf(-logits[t * E + e]));
+    s[e] = v;
+    c[e] = v + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  const int per = E / n_groups;
+  if (keep < n_groups) {
+    for (int g = lane; g < n_groups; g += 32) {
+      float b0 = -INFINITY, b1 = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = c[e];
+        if (v > b0) b1 = b0, b0 = v;
+        else if (v > b1) b1 = v;
+      }
+      gs[g] = per > 1 ? b0 + b1 : b0;
+    }
+    __syncwarp();
+    // every group but the `keep` best loses its experts: take the worst n_groups - keep out one by one (ties: the
+    // higher index goes first, so the lower index stays)
+    for (int r = 0; r < n_groups - keep; ++r) {
+      float worst = INFINITY;
+      int at = -1;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v <= worst && v != INFINITY) worst = v, at = g;      // ascending g: the highest index wins inside a lane
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, worst, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oi >= 0 && (at < 0 || ov < worst || (ov == worst && oi > at))) worst = ov, at = oi;
+      }
+      if (at >= 0) {
+        for (int e = at * per + lane; e < (at + 1) * per; e += 32) c[e] = -INFINITY;
+        if (lane == 0) gs[at] = INFINITY;   // out of the running
+      }
+      __syncwarp();
+    }
+  }
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = E;
+    for (int e = lane; e < E; e += 32)
+      if (c[e] > best) best = c[e], at = e;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
+    }
+    if (at >= E) at = 0;   // fewer candidates than `top`: cannot happen for top <= keep * per
+    const float sv = s[at];
+    sum += sv;
+    if (lane == 0) {
+      idx[t * top + k] = at;
+      weight[t * top + k] = sv;
+    }
+    __syncwarp();
+    if (lane == 0) c[at] = -INFINITY;
+    __syncwarp();
+  }
+  const float k = scale / (sum + 1e-20f);
+  __syncwarp();
+  for (int j = lane; j < top; j += 32) weight[t * top + j] *= k;
+}
+
 // grid (ceil(ff / 8), pairs): a warp computes one row of both projections of its pair's expert
 template <typename T>
 __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ wg, const T* __restrict__ wu,
                                       const int32_t* __restrict__ idx, int top, int64_t W, int64_t ff,
-                                      int64_t expert_stride, float limit, float alpha, T* __restrict__ y) {
+                                      int64_t expert_stride, float limit, float alpha, float shift, T* __restrict__ y) {
   extern __shared__ float xs[];   // [W]
   const int64_t p = blockIdx.y, t = p / top;
   const int64_t e = idx ? idx[p] : 0;
@@ -132,7 +214,7 @@ __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restri
     stf(&rb, b);
     const float g = fminf(ldf(&ra), limit);
     const float u = fminf(fmaxf(ldf(&rb), -limit), limit);
-    stf(y + p * ff + f, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+    stf(y + p * ff + f, g / (1.f + expf(-alpha * g)) * (u + shift));
   }
 }
 
@@ -229,9 +311,20 @@ extern "C" int ao_lm_router_topk_logits(const float* logits, int64_t n, int E, i
   return lm_launch_status();
 }
 
-extern "C" int ao_lm_expert_gate_up(const void* h, const void* w_gate, const void* w_up, int dt, const int32_t* idx, int64_t n,
-                                    int top, int64_t width, int64_t ff, int64_t expert_stride, float limit, float alpha, void* y,
-                                    void* stream) {
+extern "C" int ao_lm_router_group_topk_logits(const float* logits, int64_t n, int E, int top, const float* correction,
+                                              int n_groups, int keep, float scale, int32_t* idx, float* weight, void* stream) {
+  LM_CHECK_ARG(logits && idx && weight && n > 0 && E > 0 && top > 0 && n_groups > 0 && E % n_groups == 0);
+  LM_CHECK_ARG(keep > 0 && keep <= n_groups && top <= keep * (E / n_groups));
+  const size_t smem = (size_t)kWarps * (2 * E + n_groups) * sizeof(float);
+  if (smem > 48 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  router_group_topk_kernel<<<(unsigned)((n + kWarps - 1) / kWarps), kWarps * 32, smem, lm_stream(stream)>>>(
+      logits, n, E, top, correction, n_groups, keep, scale, idx, weight);
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_expert_gate_up_shift(const void* h, const void* w_gate, const void* w_up, int dt, const int32_t* idx,
+                                          int64_t n, int top, int64_t width, int64_t ff, int64_t expert_stride, float limit,
+                                          float alpha, float shift, void* y, void* stream) {
   LM_CHECK_ARG(h && w_gate && w_up && y && n > 0 && top > 0 && width > 0 && ff > 0 && n * top <= 65535);
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
@@ -241,9 +334,15 @@ extern "C" int ao_lm_expert_gate_up(const void* h, const void* w_gate, const voi
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     kern<<<grid, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_gate),
                                                         static_cast<const T*>(w_up), idx, top, width, ff, expert_stride, limit, alpha,
-                                                        static_cast<T*>(y));
+                                                        shift, static_cast<T*>(y));
   });
   return lm_launch_status();
+}
+
+extern "C" int ao_lm_expert_gate_up(const void* h, const void* w_gate, const void* w_up, int dt, const int32_t* idx, int64_t n,
+                                    int top, int64_t width, int64_t ff, int64_t expert_stride, float limit, float alpha, void* y,
+                                    void* stream) {
+  return ao_lm_expert_gate_up_shift(h, w_gate, w_up, dt, idx, n, top, width, ff, expert_stride, limit, alpha, 1.f, y, stream);
 }
 
 extern "C" int ao_lm_expert_down(const void* y, const void* w_down, int dt, const int32_t* idx, const float* weight, int64_t n,

@@ -1,0 +1,287 @@
+// Recurrences whose state is a matrix per head, S_t = a_t S_(t-1) + b_t k_t v_t^T (S: d x dv), read out as
+// o_t = S_t^T q_t + skip_h v_t.  Two mixers are this recurrence with different decays:
+//   linear attention with a fixed decay per head     a_t = decay_h, b_t = 1, q / k / v through an activation;
+//   state-space duality (selective state space)      a_t = exp(-exp(A_h) dt_t), b_t = dt_t, k = B_t, q = C_t shared by the
+//                                                    heads of a group, v = x_t, skip_h = D_h,
+// so one kernel serves both, with a and b per (row, head) in device memory or constant per head.
+//
+// The state lives in fp32 [slots][H][d][dv] and is carried from step to step; a sequence that starts at position 0 starts
+// from zeros without reading its slot.  Every product and sum is fp32, and every token is folded into the state by the
+// same instructions whether it arrives alone or inside a prompt portion, so a result does not depend on how the sequence
+// was cut into steps.
+//
+// One CTA = one segment (consecutive rows of one sequence) x one head x 32 value columns.  Lane = column, warp p owns DR
+// rows of the state in registers; tokens are staged 16 at a time in shared memory, each warp leaves its partial read-outs
+// there and the block adds them up once per 16 tokens.
+//
+// Around it: the input side of the state-space mixer (causal convolution over time with the slot's memory + SiLU,
+// softplus step sizes, decays), the convolution memory's update, and the gated group RMS norm both mixers end with.
+#include "lm_common.cuh"
+
+using namespace lm;
+
+namespace {
+
+constexpr int kTB = 16;        // tokens staged per round
+constexpr int kCols = 32;      // value columns per CTA
+
+__device__ __forceinline__ float act_apply(float v, int act) { return act == 1 ? v / (1.f + expf(-v)) : v; }
+
+struct RecArgs {
+  const float *q, *k, *v;        // rows [n][ld*]; q / k hold G groups of d, v holds H heads of dv
+  int64_t ldq, ldk, ldv;
+  int act;                       // 0: as they are, 1: SiLU on load
+  const float *a, *b;            // [n][ld_ab] per (row, head); null: a = a_head[h], b = 1
+  int64_t ld_ab;
+  const float *a_head, *skip;    // [H]; skip null: none
+  int H, G, d, dv;
+  float* state;                  // [slots][H][d][dv]
+  const int32_t *slot, *pos, *seg_first, *seg_count;
+  float* out;                    // [n][ld_out], H * dv per row
+  int64_t ld_out;
+};
+
+template <int DR>
+__global__ void __launch_bounds__(DR == 32 ? 1024 : 256) outer_recurrence_kernel(RecArgs A) {
+  extern __shared__ __align__(16) float sm[];
+  const int P = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int dp = P * DR;                       // d rounded up to what the warps cover
+  float* qs = sm;                              // [kTB][dp]
+  float* ks = qs + kTB * dp;                   // [kTB][dp]
+  float* vs = ks + kTB * dp;                   // [kTB][kCols]
+  float* ab = vs + kTB * kCols;                // [kTB][2]
+  float* op = ab + kTB * 2;                    // [P][kTB][kCols]
+  const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kCols, c = c0 + lane;
+  const int first = A.seg_first[seg], count = A.seg_count[seg];
+  const int g = h / (A.H / A.G), d = A.d, dv = A.dv;
+  const bool col = c < dv;
+  float* srow = A.state + (((int64_t)A.slot[first] * A.H + h) * d) * dv + c;
+  float S[DR];
+  const bool fresh = A.pos[first] == 0;
+#pragma unroll
+  for (int r = 0; r < DR; ++r) {
+    const int i = warp * DR + r;
+    S[r] = (!fresh && col && i < d) ? srow[(int64_t)i * dv] : 0.f;
+  }
+  const float skip = A.skip ? A.skip[h] : 0.f;
+  for (int t0 = 0; t0 < count; t0 += kTB) {
+    const int nb = min(kTB, count - t0);
+    __syncthreads();   // the previous round's read-outs are out
+    for (int i = threadIdx.x; i < nb * dp; i += blockDim.x) {
+      const int j = i / dp, e = i - j * dp;
+      const int64_t t = first + t0 + j;
+      float qv = 0.f, kv = 0.f;
+      if (e < d) {
+        qv = act_apply(A.q[t * A.ldq + (int64_t)g * d + e], A.act);
+        kv = act_apply(A.k[t * A.ldk + (int64_t)g * d + e], A.act);
+      }
+      qs[i] = qv, ks[i] = kv;
+    }
+    for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
+      const int j = i / kCols, e = i - j * kCols;
+      const int64_t t = first + t0 + j;
+      vs[i] = c0 + e < dv ? act_apply(A.v[t * A.ldv + (int64_t)h * dv + c0 + e], A.act) : 0.f;
+    }
+    for (int j = threadIdx.x; j < nb; j += blockDim.x) {
+      const int64_t t = first + t0 + j;
+      ab[2 * j] = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
+      ab[2 * j + 1] = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+    }
+    __syncthreads();
+    for (int j = 0; j < nb; ++j) {
+      const float a = ab[2 * j], bv = ab[2 * j + 1] * vs[j * kCols + lane];
+      const float4* k4 = reinterpret_cast<const float4*>(ks + j * dp + warp * DR);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + j * dp + warp * DR);
+      float o = 0.f;
+#pragma unroll
+      for (int r4 = 0; r4 < DR / 4; ++r4) {
+        const float4 kk = k4[r4], qq = q4[r4];
+        S[4 * r4 + 0] = fmaf(a, S[4 * r4 + 0], kk.x * bv);
+        S[4 * r4 + 1] = fmaf(a, S[4 * r4 + 1], kk.y * bv);
+        S[4 * r4 + 2] = fmaf(a, S[4 * r4 + 2], kk.z * bv);
+        S[4 * r4 + 3] = fmaf(a, S[4 * r4 + 3], kk.w * bv);
+        o = fmaf(S[4 * r4 + 0], qq.x, o);
+        o = fmaf(S[4 * r4 + 1], qq.y, o);
+        o = fmaf(S[4 * r4 + 2], qq.z, o);
+        o = fmaf(S[4 * r4 + 3], qq.w, o);
+      }
+      op[(warp * kTB + j) * kCols + lane] = o;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
+      const int j = i / kCols, e = i - j * kCols;
+      if (c0 + e >= dv) continue;
+      float o = skip * vs[i];
+      for (int p = 0; p < P; ++p) o += op[(p * kTB + j) * kCols + e];
+      A.out[(int64_t)(first + t0 + j) * A.ld_out + (int64_t)h * dv + c0 + e] = o;
+    }
+  }
+  if (col) {
+#pragma unroll
+    for (int r = 0; r < DR; ++r) {
+      const int i = warp * DR + r;
+      if (i < d) srow[(int64_t)i * dv] = S[r];
+    }
+  }
+}
+
+// rows of the state per warp for a key size: 8 warps up to d = 256, more warps beyond
+inline int rec_rows_per_warp(int d) { return d <= 32 ? 4 : d <= 64 ? 8 : d <= 128 ? 16 : 32; }
+inline size_t rec_smem(int P, int DR) { return ((size_t)kTB * (2 * P * DR + kCols + 2) + (size_t)P * kTB * kCols) * sizeof(float); }
+
+template <int DR>
+int launch_rec(const RecArgs& A, int n_segments, cudaStream_t st) {
+  const int P = (A.d + DR - 1) / DR;
+  const size_t smem = rec_smem(P, DR);
+  auto kern = outer_recurrence_kernel<DR>;
+  if (smem > 48 * 1024) {
+    static bool set = false;   // per instantiation
+    if (!set) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return AO_B200_ERR_CUDA;
+      set = true;
+    }
+  }
+  kern<<<dim3((unsigned)n_segments, (unsigned)A.H, (unsigned)((A.dv + kCols - 1) / kCols)), P * 32, smem, st>>>(A);
+  return lm_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Input side of the state-space mixer.  One CTA per row: the convolution channels, then the heads' step sizes.
+template <typename T>
+__global__ void ssd_prep_kernel(const float* __restrict__ proj, int64_t ld, int64_t conv_off, int64_t dt_off, int64_t channels,
+                                int taps, const T* __restrict__ conv_w, const T* __restrict__ conv_b,
+                                const float* __restrict__ conv_state, const int32_t* __restrict__ slot,
+                                const int32_t* __restrict__ pos, const int32_t* __restrict__ back, int H,
+                                const T* __restrict__ dt_bias, const T* __restrict__ a_log, float* __restrict__ conv_out,
+                                float* __restrict__ a_out, float* __restrict__ b_out) {
+  const int64_t t = blockIdx.x;
+  const int bk = back[t], p = pos[t];
+  const float* st = conv_state + (int64_t)slot[t] * (taps > 1 ? taps - 1 : 1) * channels;
+  for (int64_t c = threadIdx.x; c < channels; c += blockDim.x) {
+    float acc = conv_b ? ldf(conv_b + c) : 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int delta = taps - 1 - j;     // rows back in time
+      float v = 0.f;
+      if (delta <= bk)
+        v = proj[(t - delta) * ld + conv_off + c];
+      else if (delta <= p)
+        v = st[(int64_t)(taps - 1 - (delta - bk)) * channels + c];
+      acc = fmaf(ldf(conv_w + c * taps + j), v, acc);
+    }
+    conv_out[t * channels + c] = acc / (1.f + expf(-acc));
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float z = proj[t * ld + dt_off + h] + ldf(dt_bias + h);
+    const float step = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));      // softplus, no clamp
+    a_out[t * H + h] = expf(-expf(ldf(a_log + h)) * step);
+    b_out[t * H + h] = step;
+  }
+}
+
+// The last taps - 1 inputs of every sequence that the step touched become its convolution memory (oldest first); a
+// segment shorter than that keeps the newest of what the memory held, and zeros stand in front of position 0.
+__global__ void conv_state_save_kernel(const float* __restrict__ x, int64_t ldx, int64_t channels, int taps,
+                                       const int32_t* __restrict__ slot, const int32_t* __restrict__ pos,
+                                       const int32_t* __restrict__ back, const int32_t* __restrict__ ahead,
+                                       float* __restrict__ state) {
+  const int64_t t = blockIdx.x;
+  if (ahead[t] != 0) return;
+  const int keep = taps - 1, rows = back[t] + 1;
+  const int64_t first = t - back[t];
+  const int p0 = pos[t] - back[t];
+  float* st = state + (int64_t)slot[t] * keep * channels;
+  for (int64_t c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int j = 0; j < keep; ++j) {      // ascending: a row of the old memory is read before it is overwritten
+      const int s = rows - keep + j;      // index among the segment's rows
+      float v = 0.f;
+      if (s >= 0)
+        v = x[(first + s) * ldx + c];
+      else if (p0 + s >= 0)
+        v = st[(int64_t)(keep + s) * channels + c];
+      st[(int64_t)j * channels + c] = v;
+    }
+  }
+}
+
+// out = norm(y) * weight * sigmoid(gate)              (mode 0: the gate after the norm)
+// out = norm(y * silu(gate)) * weight                 (mode 1: the gate in front of it)
+// with the norm taken over each of `groups` equal parts of the row.  grid (rows, groups).
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gate, int64_t ldg,
+                                        int mode, int64_t width, int groups, const T* __restrict__ weight, float eps,
+                                        T* __restrict__ out) {
+  __shared__ float scratch[33];
+  const int64_t t = blockIdx.x, per = width / groups, c0 = (int64_t)blockIdx.y * per;
+  const float* yr = y + t * ldy + c0;
+  const float* gr = gate + t * ldg + c0;
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < per; c += blockDim.x) {
+    float v = yr[c];
+    if (mode == 1) {
+      const float z = gr[c];
+      v *= z / (1.f + expf(-z));
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float k = 1.f / sqrtf(ss / (float)per + eps);
+  for (int64_t c = threadIdx.x; c < per; c += blockDim.x) {
+    const float z = gr[c];
+    float v = yr[c];
+    if (mode == 1)
+      v = v * (z / (1.f + expf(-z))) * k * ldf(weight + c0 + c);
+    else
+      v = v * k * ldf(weight + c0 + c) / (1.f + expf(-z));
+    stf(out + t * width + c0 + c, v);
+  }
+}
+
+}  // namespace
+
+extern "C" int ao_lm_outer_recurrence(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                                      int act, const float* a, const float* b, int64_t ld_ab, const float* a_head,
+                                      const float* skip, int H, int G, int d, int dv, float* state, const int32_t* slot,
+                                      const int32_t* pos, const int32_t* seg_first, const int32_t* seg_count, int n_segments,
+                                      float* out, int64_t ld_out, void* stream) {
+  LM_CHECK_ARG(q && k && v && state && slot && pos && seg_first && seg_count && out && (a || a_head) && (!b || a));
+  LM_CHECK_ARG(n_segments > 0 && H > 0 && G > 0 && H % G == 0 && H <= 65535 && d > 0 && dv > 0 && (act == 0 || act == 1));
+  if (d > 1024) return AO_B200_ERR_UNSUPPORTED;
+  RecArgs A{q, k, v, ldq, ldk, ldv, act, a, b, ld_ab, a_head, skip, H, G, d, dv, state, slot, pos, seg_first, seg_count, out, ld_out};
+  const cudaStream_t st = lm_stream(stream);
+  switch (rec_rows_per_warp(d)) {
+    case 4: return launch_rec<4>(A, n_segments, st);
+    case 8: return launch_rec<8>(A, n_segments, st);
+    case 16: return launch_rec<16>(A, n_segments, st);
+    default: return launch_rec<32>(A, n_segments, st);
+  }
+}
+
+extern "C" int ao_lm_ssd_prep(const float* proj, int64_t ld, int64_t conv_off, int64_t dt_off, int64_t n, int64_t channels,
+                              int taps, const void* conv_w, const void* conv_b, int dt, const float* conv_state,
+                              const int32_t* slot, const int32_t* pos, const int32_t* back, int H, const void* dt_bias,
+                              const void* a_log, float* conv_out, float* a_out, float* b_out, void* stream) {
+  LM_CHECK_ARG(proj && conv_w && conv_state && slot && pos && back && dt_bias && a_log && conv_out && a_out && b_out);
+  LM_CHECK_ARG(n > 0 && channels > 0 && taps >= 1 && H > 0);
+  LM_DISPATCH(dt, ssd_prep_kernel<T><<<(unsigned)n, 256, 0, lm_stream(stream)>>>(
+                      proj, ld, conv_off, dt_off, channels, taps, static_cast<const T*>(conv_w), static_cast<const T*>(conv_b),
+                      conv_state, slot, pos, back, H, static_cast<const T*>(dt_bias), static_cast<const T*>(a_log), conv_out, a_out,
+                      b_out));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_conv_state_save(const float* x, int64_t ldx, int64_t n, int64_t channels, int taps, const int32_t* slot,
+                                     const int32_t* pos, const int32_t* back, const int32_t* ahead, float* state, void* stream) {
+  LM_CHECK_ARG(x && slot && pos && back && ahead && state && n > 0 && channels > 0 && taps >= 1);
+  if (taps == 1) return AO_B200_OK;   // a one-tap convolution remembers nothing
+  conv_state_save_kernel<<<(unsigned)n, 256, 0, lm_stream(stream)>>>(x, ldx, channels, taps, slot, pos, back, ahead, state);
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_gated_group_norm(const float* y, int64_t ldy, const float* gate, int64_t ldg, int mode, int64_t n,
+                                      int64_t width, int groups, const void* weight, int dt, float eps, void* out, void* stream) {
+  LM_CHECK_ARG(y && gate && weight && out && n > 0 && width > 0 && groups > 0 && groups <= 65535 && width % groups == 0);
+  LM_CHECK_ARG(mode == 0 || mode == 1);
+  LM_DISPATCH(dt, gated_group_norm_kernel<T><<<dim3((unsigned)n, (unsigned)groups), 256, 0, lm_stream(stream)>>>(
+                      y, ldy, gate, ldg, mode, width, groups, static_cast<const T*>(weight), eps, static_cast<T*>(out)));
+  return lm_launch_status();
+}

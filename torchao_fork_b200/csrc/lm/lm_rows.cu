@@ -138,19 +138,81 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t ld, int64
   for (int d = 2 * half + threadIdx.x; d < dr; d += blockDim.x) kr_cache[at * dr + d] = kv[R + d];
 }
 
+// A sublayer's result enters the residual through its own RMS norm (a weight per coordinate), and the next sublayer's
+// input norm is taken in the same pass over the row:
+//   x += y / sqrt(mean(y^2) + eps) * post_w;   x += add_rows[t];   x += add_vec;   h = x / sqrt(mean(x^2) + eps) * next_w.
+// Every part but x is optional.  The row stays in registers between the two norms (up to kPostPer values per thread).
+constexpr int kPostPer = 8;
+template <typename T, typename TY>
+__global__ void postnorm_residual_kernel(float* __restrict__ x, const TY* __restrict__ y, const T* __restrict__ post_w,
+                                         const float* __restrict__ add_rows, const T* __restrict__ add_vec,
+                                         const T* __restrict__ next_w, float eps, int64_t W, T* __restrict__ h) {
+  __shared__ float scratch[33];
+  const int64_t t = blockIdx.x;
+  float* xr = x + t * W;
+  float k = 0.f;
+  if (y) {
+    const TY* yr = y + t * W;
+    float ss = 0.f;
+    for (int64_t w = threadIdx.x; w < W; w += blockDim.x) {
+      const float v = ldf(yr + w);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    k = 1.f / sqrtf(ss / (float)W + eps);
+  }
+  const bool in_regs = W <= (int64_t)kPostPer * blockDim.x;
+  float keep[kPostPer];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPostPer; ++i) {
+    const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
+    if (w < W) {
+      float v = xr[w];
+      if (y) v = fmaf(ldf(y + t * W + w) * k, post_w ? ldf(post_w + w) : 1.f, v);
+      if (add_rows) v += add_rows[t * W + w];
+      if (add_vec) v += ldf(add_vec + w);
+      xr[w] = v;
+      keep[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+  }
+  for (int64_t w = threadIdx.x + (int64_t)kPostPer * blockDim.x; w < W; w += blockDim.x) {
+    float v = xr[w];
+    if (y) v = fmaf(ldf(y + t * W + w) * k, post_w ? ldf(post_w + w) : 1.f, v);
+    if (add_rows) v += add_rows[t * W + w];
+    if (add_vec) v += ldf(add_vec + w);
+    xr[w] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (!next_w) return;
+  ss = block_sum(ss, scratch);
+  const float kn = 1.f / sqrtf(ss / (float)W + eps);
+  if (in_regs) {
+#pragma unroll
+    for (int i = 0; i < kPostPer; ++i) {
+      const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
+      if (w < W) stf(h + t * W + w, keep[i] * kn * ldf(next_w + w));
+    }
+  } else {
+    for (int64_t w = threadIdx.x; w < W; w += blockDim.x) stf(h + t * W + w, xr[w] * kn * ldf(next_w + w));
+  }
+}
+
 template <typename T>
-__global__ void glu_act_kernel(const T* __restrict__ gu, int64_t n, int64_t ff, float limit, float alpha, T* __restrict__ y) {
+__global__ void glu_act_kernel(const T* __restrict__ gu, int64_t n, int64_t ff, float limit, float alpha, float shift,
+                               T* __restrict__ y) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n * ff) return;
   const int64_t t = i / ff, f = i - t * ff;
   const float g = fminf(ldf(gu + t * 2 * ff + f), limit);
   const float u = fminf(fmaxf(ldf(gu + t * 2 * ff + ff + f), -limit), limit);
-  stf(y + i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  stf(y + i, g / (1.f + expf(-alpha * g)) * (u + shift));
 }
 
 // bf16 rows with ff a multiple of 8: one thread makes 8 outputs from two 16-byte loads
 __global__ void glu_act_vec_kernel(const __nv_bfloat16* __restrict__ gu, int64_t n, int64_t ff, float limit, float alpha,
-                                   __nv_bfloat16* __restrict__ y) {
+                                   float shift, __nv_bfloat16* __restrict__ y) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, per = ff / 8;
   if (i >= n * per) return;
   const int64_t t = i / per, f = (i - t * per) * 8;
@@ -165,7 +227,7 @@ __global__ void glu_act_vec_kernel(const __nv_bfloat16* __restrict__ gu, int64_t
     for (int e = 0; e < 2; ++e) {
       const float gv = fminf(__uint_as_float(e ? aw[j] & 0xFFFF0000u : aw[j] << 16), limit);
       const float uv = fminf(fmaxf(__uint_as_float(e ? bw[j] & 0xFFFF0000u : bw[j] << 16), -limit), limit);
-      r[e] = gv / (1.f + expf(-alpha * gv)) * (uv + 1.f);
+      r[e] = gv / (1.f + expf(-alpha * gv)) * (uv + shift);
     }
     const __nv_bfloat162 pk = __floats2bfloat162_rn(r[0], r[1]);
     o[j] = *reinterpret_cast<const uint32_t*>(&pk);
@@ -279,16 +341,39 @@ extern "C" int ao_lm_latent_prep(const void* proj, int dt, int64_t ld, int64_t n
   return lm_launch_status();
 }
 
-extern "C" int ao_lm_glu_act(const void* gu, int dt, int64_t n, int64_t ff, float limit, float alpha, void* y, void* stream) {
+extern "C" int ao_lm_glu_act_shift(const void* gu, int dt, int64_t n, int64_t ff, float limit, float alpha, float shift, void* y,
+                                   void* stream) {
   LM_CHECK_ARG(gu && y && n > 0 && ff > 0);
   if (dt == AO_LM_BF16 && ff % 8 == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
     glu_act_vec_kernel<<<(unsigned)((n * (ff / 8) + 255) / 256), 256, 0, lm_stream(stream)>>>(
-        static_cast<const __nv_bfloat16*>(gu), n, ff, limit, alpha, static_cast<__nv_bfloat16*>(y));
+        static_cast<const __nv_bfloat16*>(gu), n, ff, limit, alpha, shift, static_cast<__nv_bfloat16*>(y));
     return lm_launch_status();
   }
   const unsigned grid = (unsigned)((n * ff + 255) / 256);
-  LM_DISPATCH(dt, glu_act_kernel<T><<<grid, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(gu), n, ff, limit, alpha,
+  LM_DISPATCH(dt, glu_act_kernel<T><<<grid, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(gu), n, ff, limit, alpha, shift,
                                                                          static_cast<T*>(y)));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_glu_act(const void* gu, int dt, int64_t n, int64_t ff, float limit, float alpha, void* y, void* stream) {
+  return ao_lm_glu_act_shift(gu, dt, n, ff, limit, alpha, 1.f, y, stream);
+}
+
+extern "C" int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const void* post_w, const float* add_rows,
+                                       const void* add_vec, const void* next_w, int dt, float eps, int64_t n, int64_t width,
+                                       void* h, void* stream) {
+  LM_CHECK_ARG(x && n > 0 && width > 0 && (!next_w || h) && (y_dt == AO_LM_BF16 || y_dt == AO_LM_F32));
+  const unsigned threads = row_threads(n, width);
+  LM_DISPATCH(dt, {
+    if (y_dt == AO_LM_F32)
+      postnorm_residual_kernel<T, float><<<(unsigned)n, threads, 0, lm_stream(stream)>>>(
+          x, static_cast<const float*>(y), static_cast<const T*>(post_w), add_rows, static_cast<const T*>(add_vec),
+          static_cast<const T*>(next_w), eps, width, static_cast<T*>(h));
+    else
+      postnorm_residual_kernel<T, __nv_bfloat16><<<(unsigned)n, threads, 0, lm_stream(stream)>>>(
+          x, static_cast<const __nv_bfloat16*>(y), static_cast<const T*>(post_w), add_rows, static_cast<const T*>(add_vec),
+          static_cast<const T*>(next_w), eps, width, static_cast<T*>(h));
+  });
   return lm_launch_status();
 }
 
