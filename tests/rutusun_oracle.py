@@ -79,7 +79,8 @@ def attention_mixer(cfg, m, w, p, h):
     v = linear(h, w, p + "v", p + "v.b").view(T, G, dv)
     q = rms_norm(q, _w(w, p + "q.norm"), eps)
     k = _r(rms_norm(k, _w(w, p + "k.norm"), eps))
-    q = q * query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"]).view(T, 1, 1)
+    if m.get("q_temp"):
+        q = q * query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"]).view(T, 1, 1)
     o = sink_attention(q, k, v, _w(w, p + "sink"), m["scale"])
     return linear(o.reshape(T, H * dv), w, p + "o", p + "o.b")
 
@@ -227,3 +228,132 @@ def forward(cfg, w, tokens, layer_out=None):
             x = run(i, x)
     x = rms_norm(x, _w(w, "final.norm"), cfg["norm"]["eps"])
     return _r(x) @ _w(w, "head").T
+
+
+def rounding_noise(cfg, w, tokens, measure):
+    """measure(exact logits, logits of the run that rounds to bfloat16 wherever a bfloat16 implementation does)."""
+    global ROUND_BF16
+    exact = forward(cfg, w, tokens)
+    ROUND_BF16 = True
+    try:
+        rounded = forward(cfg, w, tokens)
+    finally:
+        ROUND_BF16 = False
+    return measure(exact, rounded)
+
+
+def greedy(cfg, w, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+# ------------------------------------------------------------------------------------------------ test models
+def attention_layer(heads=4, kv_heads=2, dim=8, vdim=12, scale=0.4, coef=0.5, every=16, mlp=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if coef is not None:
+        m["q_temp"] = {"coef": coef, "every": every}
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def lightning_layer(heads=3, dim=8, vdim=12, decay=None, mlp=None):
+    decay = decay or [math.exp(-1.0 / (1.5 + 6.0 * h)) for h in range(heads)]
+    return {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}, "mlp": mlp}
+
+
+def mamba2_layer(heads=4, vdim=6, state=10, groups=2, conv=4, norm_groups=2, mlp=None):
+    return {"type": "mamba2", "mlp": mlp,
+            "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}}
+
+
+def dense(ff=40):
+    return {"kind": "dense", "ff": ff}
+
+
+def mixture(experts=8, top=2, ff=16, groups=4, keep=2, scale=1.5, shared=24):
+    f = {"kind": "moe", "expert": {"ff": ff},
+         "router": {"experts": experts, "top": top, "scale": scale, "groups": {"count": groups, "keep": keep}}}
+    if shared:
+        f["shared"] = {"ff": shared}
+    return f
+
+
+def model_config(layers, width=32, vocab=61, loop=None, eps=1e-5):
+    cfg = {"architecture": "Rutusun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def random_weights(cfg, seed=0, dtype=torch.bfloat16):
+    """Every tensor the configuration names, seeded, sized so that each mechanism moves the logits."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def mat(o, i, s=1.0):
+        return torch.randn(o, i, generator=g, dtype=torch.float32) * (s / math.sqrt(i))
+
+    def vec(n, mean=0.0, s=1.0):
+        n = n if isinstance(n, tuple) else (n,)
+        return mean + s * torch.randn(*n, generator=g, dtype=torch.float32)
+
+    def unit(p, ff):
+        w[p + "gate"], w[p + "up"], w[p + "down"] = mat(ff, W, 1.5), mat(ff, W, 1.5), mat(W, ff, 1.5)
+
+    w = {"embed": vec((V, W), 0.0, 1.0), "head": mat(V, W, 2.0), "final.norm": vec(W, 1.0, 0.2)}
+    if cfg.get("loop"):
+        w["loop.step"] = vec((cfg["loop"]["times"], W), 0.0, 0.5)
+    for i, lay in enumerate(cfg["layers"]):
+        p, q, m = f"l{i}.", f"l{i}.mix.", lay["mixer"]
+        w[p + "norm1"], w[p + "norm1b"] = vec(W, 1.0, 0.2), vec(W, 1.0, 0.2)
+        if lay["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            w[q + "q"], w[q + "k"], w[q + "v"], w[q + "o"] = mat(H * d, W, 2.0), mat(G * d, W, 2.0), mat(G * dv, W), mat(W, H * dv)
+            w[q + "q.b"], w[q + "k.b"], w[q + "v.b"], w[q + "o.b"] = vec(H * d, 0.0, 0.3), vec(G * d, 0.0, 0.3), vec(G * dv, 0.0, 0.3), vec(W, 0.0, 0.3)
+            w[q + "q.norm"], w[q + "k.norm"], w[q + "sink"] = vec(d, 1.0, 0.3), vec(d, 1.0, 0.3), vec(H, 0.5, 1.0)
+        elif lay["type"] == "lightning":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            w[q + "q"], w[q + "k"], w[q + "v"], w[q + "g"] = mat(H * d, W, 2.0), mat(H * d, W, 2.0), mat(H * dv, W, 2.0), mat(H * dv, W)
+            w[q + "norm"], w[q + "o"] = vec(H * dv, 1.0, 0.2), mat(W, H * dv)
+        else:
+            H, dv, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, ch = H * dv, H * dv + 2 * G * N
+            w[q + "in"] = mat(2 * inner + 2 * G * N + H, W, 1.5)
+            w[q + "conv"], w[q + "conv.b"] = vec((ch, m["conv"]), 0.25, 0.4), vec(ch, 0.0, 0.2)
+            w[q + "dt_bias"], w[q + "A_log"], w[q + "D"] = vec(H, -1.5, 1.0), vec(H, -1.0, 0.7), vec(H, 1.0, 0.3)
+            w[q + "norm"], w[q + "o"] = vec(inner, 1.0, 0.2), mat(W, inner)
+        f = lay.get("mlp")
+        if not f:
+            continue
+        w[p + "norm2"], w[p + "norm2b"] = vec(W, 1.0, 0.2), vec(W, 1.0, 0.2)
+        if f["kind"] == "dense":
+            unit(p + "mlp.", f["ff"])
+        else:
+            E = f["router"]["experts"]
+            for e in range(E):
+                unit(f"{p}mlp.e{e}.", f["expert"]["ff"])
+            w[p + "mlp.router"], w[p + "mlp.correction"] = mat(E, W, 3.0), vec(E, -0.3, 0.4)
+            if f.get("shared"):
+                unit(p + "mlp.shared.", f["shared"]["ff"])
+    return {k: v.to(dtype) for k, v in w.items()}
+
+
+def write_checkpoint(folder, cfg, w):
+    """config.json + model.safetensors (8-byte little-endian header length, JSON header, raw data) in `folder`."""
+    import json
+    import os
+    import struct
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    names = {torch.bfloat16: "BF16", torch.float32: "F32", torch.int32: "I32"}
+    header, blobs, at = {}, [], 0
+    for name, t in w.items():
+        raw = t.contiguous().reshape(-1).view(torch.uint8).numpy().tobytes()
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
