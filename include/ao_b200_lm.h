@@ -268,13 +268,20 @@ AO_B200_API int ao_lm_sink_attention_prompt(const float* qn, const void* kn, con
 /* Matrix-state recurrence per head: S_t = a_t S_(t-1) + b_t k_t v_t^T (S: d x dv, fp32 state[slots][H][d][dv], zeros at
  * position 0), out[t][h] = S_t^T q_t + skip[h] v_t (fp32).  q and k rows hold G groups of d (head h reads group
  * h / (H / G)), v rows H heads of dv; act = 1 applies SiLU to q, k and v on load.  a, b: fp32 [n][ld_ab] per (row, head);
- * a == null: a_t = a_head[h] and b_t = 1 (a fixed decay per head).  seg_first / seg_count: the step's segments (runs of
- * consecutive rows of one sequence), whole. */
+ * a == null: a_t = a_head[h] and b_t = 1 (a fixed decay per head).
+ * seg_tile0 == null: seg_first / seg_count are the step's segments (runs of consecutive rows of one sequence), whole; one
+ * launch, a CTA walks its segment row by row (decoded tokens, short portions).
+ * Otherwise seg_first / seg_count are TILES of rows inside segments and segment s of n_whole_segments owns tiles
+ * seg_tile0[s] .. + seg_tiles[s] - 1: three launches (every tile from a zero state; the tiles' start states carried
+ * through each segment, element by element; the read-out of each tile's start state added to its rows), with a workspace
+ * of ao_lm_outer_recurrence_workspace_bytes.  Both forms compute the same sums in fp32; they differ in rounding only. */
+AO_B200_API int64_t ao_lm_outer_recurrence_workspace_bytes(int n_tiles, int64_t n, int H, int d, int dv);
 AO_B200_API int ao_lm_outer_recurrence(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                                        int act, const float* a, const float* b, int64_t ld_ab, const float* a_head,
                                        const float* skip, int H, int G, int d, int dv, float* state, const int32_t* slot,
                                        const int32_t* pos, const int32_t* seg_first, const int32_t* seg_count, int n_segments,
-                                       float* out, int64_t ld_out, void* stream);
+                                       const int32_t* seg_tile0, const int32_t* seg_tiles, int n_whole_segments, int64_t n,
+                                       float* workspace, float* out, int64_t ld_out, void* stream);
 
 /* Input side of a state-space mixer, from an fp32 projection row: conv_out[t][c] = silu(conv_b[c] + sum_j conv_w[c][j] *
  * u(t - (taps - 1 - j))) over the `channels` values at conv_off (inputs in front of the step from conv_state[slot][taps - 1]

@@ -123,9 +123,10 @@ def test_query_key_preparation_bias_weight_and_temperature_steps(H, G, d, dv, ev
     k_ref = O.rms_norm(k, kw.double(), eps)
     v_ref = (proj[:, (H + G) * d:(H + G) * d + G * dv] + vb).double()
     pd, dev = proj.cuda(), [t.cuda() for t in (qb, kb, vb, qw, kw)]
+    posd = _i32(pos)
     qn, kn, vn = torch.empty(n, H, d, device="cuda"), torch.empty(n, G, d, device="cuda"), torch.empty(n, G * dv, device="cuda")
     lib.lm_check(L.ao_lm_qk_norm_prep(pd.data_ptr(), ld, 0, H * d, (H + G) * d, *[t.data_ptr() for t in dev], coef, every,
-                                      _i32(pos).data_ptr(), n, H, G, d, dv, eps, lib.DT_F32, qn.data_ptr(), kn.data_ptr(),
+                                      posd.data_ptr(), n, H, G, d, dv, eps, lib.DT_F32, qn.data_ptr(), kn.data_ptr(),
                                       vn.data_ptr(), _st()), "qk_norm_prep")
     assert _close(qn, q_ref) and _close(kn, k_ref) and _close(vn, v_ref)
     # no temperature, no weights, no biases: plain unit-RMS rows
@@ -217,12 +218,16 @@ def test_sink_attention_one_dominant_key_near_far_and_in_the_future(tensor, key,
     assert float(big.abs().max()) < 1e-6
 
 
-def _recurrence(q, k, v, a, b, a_head, skip, act, cuts, G, slots=3, slot=2, batch_with=None):
-    """The kernel over one sequence in portions; q / k [T][G][d], v [T][H][dv], a / b [T][H] or None."""
+def _recurrence(q, k, v, a, b, a_head, skip, act, cuts, G, slots=3, slot=2, tile=0):
+    """The kernel over one sequence in portions; q / k [T][G][d], v [T][H][dv], a / b [T][H] or None.  tile > 0: portions
+    longer than that run in the tiled form."""
+    from torchao_fork_b200._models.segment_step import scan_tiles
     lib, L = _lm()
     T, H, dv = v.shape
     d = q.shape[2]
     state = torch.full((slots, H, d, dv), 123.0, device="cuda")       # a freed slot's leftovers: not read at position 0
+    ahd = a_head.float().cuda() if a_head is not None else None        # held: a pointer outlives no temporary
+    skd = skip.float().cuda() if skip is not None else None
     outs, at = [], 0
     for c in cuts:
         sl, ps, bk, ah, sf, sc = _rows([(slot, at, c)])
@@ -230,12 +235,19 @@ def _recurrence(q, k, v, a, b, a_head, skip, act, cuts, G, slots=3, slot=2, batc
         ad = a[at:at + c].float().cuda().contiguous() if a is not None else None
         bd = b[at:at + c].float().cuda().contiguous() if b is not None else None
         o = torch.empty(c, H * dv, device="cuda")
+        n_seg, s0, sn, n_whole, ws = 1, None, None, 0, None
+        if tile and c > tile:
+            tf, tc, t0, tn = scan_tiles(np.array([0]), np.array([c]), tile)
+            sf, sc, s0, sn, n_seg, n_whole = _i32(tf.tolist()), _i32(tc.tolist()), _i32(t0.tolist()), _i32(tn.tolist()), len(tf), 1
+            ws = torch.empty(int(L.ao_lm_outer_recurrence_workspace_bytes(n_seg, c, H, d, dv)) // 4, device="cuda")
         lib.lm_check(L.ao_lm_outer_recurrence(qd.data_ptr(), G * d, kd.data_ptr(), G * d, vd.data_ptr(), H * dv, act,
                                               ad.data_ptr() if a is not None else None, bd.data_ptr() if b is not None else None, H,
-                                              a_head.float().cuda().data_ptr() if a_head is not None else None,
-                                              skip.float().cuda().data_ptr() if skip is not None else None, H, G, d, dv,
-                                              state.data_ptr(), sl.data_ptr(), ps.data_ptr(), sf.data_ptr(), sc.data_ptr(), 1,
-                                              o.data_ptr(), H * dv, _st()), "outer_recurrence")
+                                              ahd.data_ptr() if ahd is not None else None,
+                                              skd.data_ptr() if skd is not None else None, H, G, d, dv,
+                                              state.data_ptr(), sl.data_ptr(), ps.data_ptr(), sf.data_ptr(), sc.data_ptr(), n_seg,
+                                              s0.data_ptr() if s0 is not None else None, sn.data_ptr() if sn is not None else None,
+                                              n_whole, c, ws.data_ptr() if ws is not None else None, o.data_ptr(), H * dv, _st()),
+                     "outer_recurrence")
         outs.append(o.cpu().view(c, H, dv))
         at += c
     return torch.cat(outs)
@@ -252,6 +264,8 @@ def test_matrix_state_recurrence_both_forms_in_portions(H, G, d, dv):
         + skip.double().view(1, H, 1) * v.double()
     for cuts in ([T], [1] * T, [2, 3, 16, 1, 17, 15, 16]):
         assert _close(_recurrence(q, k, v, a, b, None, skip, 0, cuts, G), ref, 3e-5), cuts
+    for tile, cuts in ((16, [T]), (5, [3, 40, 27]), (64, [1, 69]), (3, [35, 35])):      # the tiled form, tiles cut anywhere
+        assert _close(_recurrence(q, k, v, a, b, None, skip, 0, cuts, G, tile=tile), ref, 3e-5), (tile, cuts)
     if H == G:
         # linear-attention form: a fixed decay per head, SiLU on load
         decay = torch.rand(H, generator=g) * 0.4 + 0.6
@@ -259,6 +273,7 @@ def test_matrix_state_recurrence_both_forms_in_portions(H, G, d, dv):
                                          torch.ones(T, H, dtype=F64))
         for cuts in ([T], [33, 1, 1, 35]):
             assert _close(_recurrence(q, k, v, None, None, decay, None, 1, cuts, G), ref, 3e-5), cuts
+            assert _close(_recurrence(q, k, v, None, None, decay, None, 1, cuts, G, tile=7), ref, 3e-5), cuts
 
 
 def test_matrix_state_recurrence_remembers_the_first_token_and_batches_segments():
@@ -278,11 +293,27 @@ def test_matrix_state_recurrence_remembers_the_first_token_and_batches_segments(
     cat = lambda ts: torch.cat([t.reshape(t.shape[0], -1) for t in ts]).float().cuda().contiguous()
     qd, kd, vd = cat(q), cat(k), cat(v)
     state = torch.zeros(3, H, d, dv, device="cuda")
+    ddec0 = decay.cuda()
     o = torch.empty(48, H * dv, device="cuda")
     lib.lm_check(L.ao_lm_outer_recurrence(qd.data_ptr(), H * d, kd.data_ptr(), H * d, vd.data_ptr(), H * dv, 0, None, None, 0,
-                                          decay.cuda().data_ptr(), None, H, H, d, dv, state.data_ptr(), sl.data_ptr(), ps.data_ptr(),
-                                          sf.data_ptr(), sc.data_ptr(), 3, o.data_ptr(), H * dv, _st()), "outer_recurrence")
+                                          ddec0.data_ptr(), None, H, H, d, dv, state.data_ptr(), sl.data_ptr(), ps.data_ptr(),
+                                          sf.data_ptr(), sc.data_ptr(), 3, None, None, 0, 48, None, o.data_ptr(), H * dv, _st()),
+                 "outer_recurrence")
     assert _close(o.cpu().view(48, H, dv), torch.cat(refs), 3e-5)
+    # the same three in the tiled form: 6-row tiles, segments of 7, 1 and 2 tiles; slot 1 continues a state, the others start
+    from torchao_fork_b200._models.segment_step import scan_tiles
+    tf, tc, s0, sn = scan_tiles(np.array([0, 40, 41]), np.array([40, 1, 7]), 6)
+    dtf, dtc, ds0, dsn, ddec = _i32(tf.tolist()), _i32(tc.tolist()), _i32(s0.tolist()), _i32(sn.tolist()), decay.cuda()
+    state2 = torch.full((3, H, d, dv), 9.0, device="cuda")
+    ws = torch.empty(int(L.ao_lm_outer_recurrence_workspace_bytes(len(tf), 48, H, d, dv)) // 4, device="cuda")
+    o2 = torch.empty(48, H * dv, device="cuda")
+    lib.lm_check(L.ao_lm_outer_recurrence(qd.data_ptr(), H * d, kd.data_ptr(), H * d, vd.data_ptr(), H * dv, 0, None, None, 0,
+                                          ddec.data_ptr(), None, H, H, d, dv, state2.data_ptr(), sl.data_ptr(), ps.data_ptr(),
+                                          dtf.data_ptr(), dtc.data_ptr(), len(tf), ds0.data_ptr(), dsn.data_ptr(), 3, 48, ws.data_ptr(),
+                                          o2.data_ptr(), H * dv, _st()),
+                 "outer_recurrence")
+    assert _close(o2.cpu().view(48, H, dv), torch.cat(refs), 3e-5)
+    assert _close(state2, state, 3e-5)
 
 
 @pytest.mark.parametrize("taps", [4, 1, 2, 7])
@@ -472,6 +503,11 @@ def test_pieces_cut_inside_a_step_and_both_expert_paths(monkeypatch):
     both = m.step_engine.step([(m.states.slot_of("c"), toks[:40]), (m.states.slot_of("d"), toks[:9])], [[39, 3], [8]])
     assert _err(both, ref[[39, 3, 8]]) <= F32_TOL
     monkeypatch.setattr(S, "MAX_STEP_TOKENS", 4096)
+    monkeypatch.setattr(S, "REC_TILE", 4)           # the matrix-state recurrences in their tiled form, 4-row tiles
+    both = m.step_engine.step([(m.states.slot_of("t1"), toks[:40]), (m.states.slot_of("t2"), toks[:3])], "all")
+    both2 = m.step_engine.step([(m.states.slot_of("t2"), toks[3:41]), (m.states.slot_of("t1"), toks[40:41])], "all")
+    assert _err(torch.cat([both[:40], both2[38:]]), ref[:41]) <= F32_TOL and _err(torch.cat([both[40:], both2[:38]]), ref[:41]) <= F32_TOL
+    monkeypatch.setattr(S, "REC_TILE", 64)
     for limit in (0, 10 ** 9):                      # experts as sorted rows around GEMMs for every step / as matrix-vector kernels
         monkeypatch.setattr(R, "MOE_GEMV_TOKENS", limit)
         got = m.step_engine.step([(m.states.slot_of(("e", limit)), toks)], "all")

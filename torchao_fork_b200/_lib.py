@@ -179,8 +179,9 @@ LM_SIGNATURES = {
                              _i32, _i32, _i32, _f32, _f32, _f32, _i32, _vp, _i64, _vp, _i64, _vp],
     "ao_lm_sink_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                                     _i32, _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
+    "ao_lm_outer_recurrence_workspace_bytes": [_i32, _i64, _i32, _i32, _i32],
     "ao_lm_outer_recurrence": [_vp, _i64, _vp, _i64, _vp, _i64, _i32, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp,
-                               _vp, _vp, _vp, _i32, _vp, _i64, _vp],
+                               _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i64, _vp, _vp, _i64, _vp],
     "ao_lm_ssd_prep": [_vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp,
                        _vp],
     "ao_lm_conv_state_save": [_vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -189,7 +190,7 @@ LM_SIGNATURES = {
     "ao_lm_glu_act_shift": [_vp, _i32, _i64, _i64, _f32, _f32, _f32, _vp, _vp],
     "ao_lm_expert_gate_up_shift": [_vp, _vp, _vp, _i32, _vp, _i64, _i32, _i64, _i64, _i64, _f32, _f32, _f32, _vp, _vp],
 }
-_LM_RESTYPES = {"ao_lm_last_cuda_error": ctypes.c_char_p, "ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64,
+_LM_RESTYPES = {"ao_lm_last_cuda_error": ctypes.c_char_p, "ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64, "ao_lm_outer_recurrence_workspace_bytes": _i64,
                 "ao_lm_chunk_attention_workspace_bytes": _i64}
 _lm = None
 _LM_ERRORS = {1: "invalid argument", 2: "unsupported shape", 3: "CUDA launch failed", 4: "workspace too small"}

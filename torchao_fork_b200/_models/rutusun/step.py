@@ -22,9 +22,6 @@ storage types.
 `StepEngine.step` is what prefill, the trace runner and tests call; `GraphDecodeEngine` wraps the same layer loop for
 one token per sequence with all metadata in device memory, captured into a CUDA graph.
 """
-import math
-from typing import Optional
-
 import torch
 
 from ... import _lib
@@ -38,6 +35,8 @@ _INF = float("inf")
 
 
 class StepEngine(SegmentStepEngine):
+    matrix_recurrences = True       # the step's metadata carries tiles for the tiled form of `outer_recurrence`
+
     def __init__(self, model: Rutusun):
         super().__init__(model)
         # the work in order, with what stands between two sublayers resolved once: (layer run, pass vectors in front of it)
@@ -123,6 +122,23 @@ class StepEngine(SegmentStepEngine):
         self.launches = launches
         return x
 
+    def _recurrence(self, q, ldq, k, ldk, v, ldv, act, a, b, a_head, skip, H, G, d, dv, rs, meta: StepMeta, rec, st) -> int:
+        """`outer_recurrence` over the step: whole segments in one launch, or — when a segment is longer than a tile — the
+        tiled form in three.  q, k, v, a, b: device addresses."""
+        L = self.L
+        if meta.rec is None:
+            sf, sc, ns = meta.seg
+            _lib.lm_check(L.ao_lm_outer_recurrence(q, ldq, k, ldk, v, ldv, act, a, b, H, a_head, skip, H, G, d, dv, _p(rs.mat.s),
+                                                   _p(meta.slot), _p(meta.pos), _p(sf), _p(sc), ns, None, None, 0, meta.n, None,
+                                                   _p(rec), H * dv, st), "outer_recurrence")
+            return 1
+        tf, tc, nt, s0, sn, nseg = meta.rec
+        ws = torch.empty(int(L.ao_lm_outer_recurrence_workspace_bytes(nt, meta.n, H, d, dv)) // 4, dtype=torch.float32, device=self.dev)
+        _lib.lm_check(L.ao_lm_outer_recurrence(q, ldq, k, ldk, v, ldv, act, a, b, H, a_head, skip, H, G, d, dv, _p(rs.mat.s),
+                                               _p(meta.slot), _p(meta.pos), _p(tf), _p(tc), nt, _p(s0), _p(sn), nseg, meta.n, _p(ws),
+                                               _p(rec), H * dv, st), "outer_recurrence")
+        return 3
+
     def _attention(self, lay, a, rs, h, meta: StepMeta, st):
         """Causal attention with a sink over the slot's cache and the step's rows -> (fp32 [n][W], launches)."""
         L, dt, dev, tdt = self.L, self.dt, self.dev, self.m.dtype
@@ -160,15 +176,13 @@ class StepEngine(SegmentStepEngine):
         H, d, dv, n = a.heads, a.dim, a.vdim, meta.n
         proj = self._mm_f32(h, lay.w_in)
         base, ld = proj.data_ptr(), lay.ld
-        sf, sc, ns = meta.seg
         rec = torch.empty(n, H * dv, dtype=torch.float32, device=dev)
-        _lib.lm_check(L.ao_lm_outer_recurrence(base + 4 * lay.q_off, ld, base + 4 * lay.k_off, ld, base + 4 * lay.v_off, ld, 1, None,
-                                               None, 0, _p(lay.decay), None, H, H, d, dv, _p(rs.mat.s), _p(meta.slot), _p(meta.pos),
-                                               _p(sf), _p(sc), ns, _p(rec), H * dv, st), "outer_recurrence")
+        c = self._recurrence(base + 4 * lay.q_off, ld, base + 4 * lay.k_off, ld, base + 4 * lay.v_off, ld, 1, None, None,
+                             _p(lay.decay), None, H, H, d, dv, rs, meta, rec, st)
         o = torch.empty(n, H * dv, dtype=tdt, device=dev)
         _lib.lm_check(L.ao_lm_gated_group_norm(_p(rec), H * dv, base + 4 * lay.g_off, ld, 0, n, H * dv, 1, _p(lay.mix_norm), dt,
                                                self.cfg.norm_eps, _p(o), st), "gated_group_norm")
-        return self._mm_f32(o, lay.w_out), 4
+        return self._mm_f32(o, lay.w_out), 3 + c
 
     def _mamba2(self, lay, a, rs, h, meta: StepMeta, st):
         """Selective state space in its matrix-state form -> (fp32 [n][W], launches)."""
@@ -184,16 +198,14 @@ class StepEngine(SegmentStepEngine):
                                        _p(ab[0]), _p(ab[1]), st), "ssd_prep")
         _lib.lm_check(L.ao_lm_conv_state_save(base + 4 * inner, ld, n, ch, a.conv, _p(meta.slot), _p(meta.pos), _p(meta.back),
                                               _p(meta.ahead), _p(rs.conv.x), st), "conv_state_save")
-        sf, sc, ns = meta.seg
         xb = xbc.data_ptr()
         rec = torch.empty(n, inner, dtype=torch.float32, device=dev)
-        _lib.lm_check(L.ao_lm_outer_recurrence(xb + 4 * (inner + G * N), ch, xb + 4 * inner, ch, xb, ch, 0, _p(ab[0]), _p(ab[1]), H,
-                                               None, _p(lay.skip), H, G, N, dv, _p(rs.mat.s), _p(meta.slot), _p(meta.pos), _p(sf),
-                                               _p(sc), ns, _p(rec), inner, st), "outer_recurrence")
+        c = self._recurrence(xb + 4 * (inner + G * N), ch, xb + 4 * inner, ch, xb, ch, 0, _p(ab[0]), _p(ab[1]), None, _p(lay.skip),
+                             H, G, N, dv, rs, meta, rec, st)
         o = torch.empty(n, inner, dtype=tdt, device=dev)
         _lib.lm_check(L.ao_lm_gated_group_norm(_p(rec), inner, base, ld, 1, n, inner, a.norm_groups, _p(lay.mix_norm), dt,
                                                self.cfg.norm_eps, _p(o), st), "gated_group_norm")
-        return self._mm_f32(o, lay.w_out), 6
+        return self._mm_f32(o, lay.w_out), 5 + c
 
     def _feed_forward(self, lay, f, h, n, st):
         """-> (fp32 [n][W], launches)"""

@@ -22,6 +22,8 @@ SCAN_TILE = 32
 # head sizes it covers); decoded tokens and short portions use the fp32 kernel, which shares a key block between the
 # few rows of a tile and all query heads of a key/value head
 PROMPT_MIN_ROWS = 16
+# rows of a tile of a matrix-state recurrence: a step with a longer segment runs the recurrence in its tiled form
+REC_TILE = 64
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -39,6 +41,7 @@ class StepMeta:
     scan: tuple          # (tile_first, tile_count, n_tiles, seg_tile0 | None, seg_tiles | None, n_segments)
     attn: Dict[tuple, tuple]   # attention shape -> (tile_first, tile_count, n_tiles, tensor-core form?)
     seg: tuple           # (first row, rows, n) of the step's segments, whole
+    rec: Optional[tuple] = None   # tiles of the matrix-state recurrences (as `scan`), when some segment is longer than one tile
 
 
 def segments_of(slot: np.ndarray, pos: np.ndarray):
@@ -173,6 +176,9 @@ class SegmentStepEngine:
         for key in sorted(set(meta_shapes.values())):
             attn_np[key] = chunk_tiles(starts, counts, pos, key[0], key[1])
             parts += list(attn_np[key])
+        rec = scan_tiles(starts, counts, REC_TILE) if getattr(self, "matrix_recurrences", False) else None
+        if rec is not None and rec[2] is not None:
+            parts += list(rec)
         packed = torch.from_numpy(np.concatenate(parts)).to(self.dev, non_blocking=True)
         o = [0]
 
@@ -197,6 +203,8 @@ class SegmentStepEngine:
             k = len(attn_np[key][0])
             tables[key] = (take(k), take(k), k, key[2])
         meta.attn = {shape: tables[key] for shape, key in meta_shapes.items()}
+        if rec is not None and rec[2] is not None:
+            meta.rec = (take(len(rec[0])), take(len(rec[0])), len(rec[0]), take(len(rec[2])), take(len(rec[2])), len(rec[2]))
         return d_tok, meta
 
     def _run(self, tok: np.ndarray, slot: np.ndarray, pos: np.ndarray) -> torch.Tensor:

@@ -36,12 +36,42 @@ struct RecArgs {
   const float *a_head, *skip;    // [H]; skip null: none
   int H, G, d, dv;
   float* state;                  // [slots][H][d][dv]
-  const int32_t *slot, *pos, *seg_first, *seg_count;
+  const int32_t *slot, *pos, *seg_first, *seg_count;   // whole segments, or (tiled form) tiles of rows inside segments
   float* out;                    // [n][ld_out], H * dv per row
   int64_t ld_out;
+  // tiled form: per tile the state it builds from zero, the state it starts from, and per row the product of the decays
+  // from its tile's first row on
+  float *ws_local, *ws_start, *pcum;
+  const int32_t *seg_tile0, *seg_tiles;
 };
 
-template <int DR>
+// rows [row0, row0 + nb) of src (row stride ld, `wd` values per row) -> dst[j][wp], zeros beyond wd; a warp per row
+__device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_t ld, int64_t row0, int nb, int wd, int wp,
+                                           int act, float* __restrict__ dst) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const bool vec = (wd & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  for (int j = warp; j < nb; j += nw) {
+    const float* r = src + (row0 + j) * ld;
+    float* o = dst + j * wp;
+    if (vec) {
+      for (int e = lane * 4; e < wp; e += 128) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < wd) {
+          x = *reinterpret_cast<const float4*>(r + e);
+          x.x = act_apply(x.x, act), x.y = act_apply(x.y, act), x.z = act_apply(x.z, act), x.w = act_apply(x.w, act);
+        }
+        *reinterpret_cast<float4*>(o + e) = x;
+      }
+    } else {
+      for (int e = lane; e < wp; e += 32) o[e] = e < wd ? act_apply(r[e], act) : 0.f;
+    }
+  }
+}
+
+// MODE 0: whole segments on the slots' state.  MODE 1 (tiled form, first pass): a tile of rows from a zero state; the
+// state it ends with goes to ws_local, the running product of its decays to pcum.  MODE 2 (third pass): the read-out of
+// the state the tile starts from (ws_start, made by the carry pass), scaled by the decays up to each row, added to out.
+template <int DR, int MODE>
 __global__ void __launch_bounds__(DR == 32 ? 1024 : 256) outer_recurrence_kernel(RecArgs A) {
   extern __shared__ __align__(16) float sm[];
   const int P = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -55,68 +85,85 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256) outer_recurrence_kernel
   const int first = A.seg_first[seg], count = A.seg_count[seg];
   const int g = h / (A.H / A.G), d = A.d, dv = A.dv;
   const bool col = c < dv;
-  float* srow = A.state + (((int64_t)A.slot[first] * A.H + h) * d) * dv + c;
+  float* srow = MODE == 0 ? A.state + (((int64_t)A.slot[first] * A.H + h) * d) * dv + c
+                          : (MODE == 1 ? A.ws_local : A.ws_start) + (((int64_t)seg * A.H + h) * d) * dv + c;
   float S[DR];
-  const bool fresh = A.pos[first] == 0;
+  const bool fresh = MODE == 1 || (MODE == 0 && A.pos[first] == 0);
 #pragma unroll
   for (int r = 0; r < DR; ++r) {
     const int i = warp * DR + r;
     S[r] = (!fresh && col && i < d) ? srow[(int64_t)i * dv] : 0.f;
   }
-  const float skip = A.skip ? A.skip[h] : 0.f;
+  const float skip = (MODE != 2 && A.skip) ? A.skip[h] : 0.f;
+  if (MODE == 1 && blockIdx.z == 0 && threadIdx.x == 0) {   // the decays' running product, once per (tile, head)
+    float pr = 1.f;
+    for (int j = 0; j < count; ++j) {
+      pr *= A.a ? A.a[(int64_t)(first + j) * A.ld_ab + h] : A.a_head[h];
+      A.pcum[(int64_t)(first + j) * A.H + h] = pr;
+    }
+  }
   for (int t0 = 0; t0 < count; t0 += kTB) {
     const int nb = min(kTB, count - t0);
     __syncthreads();   // the previous round's read-outs are out
-    for (int i = threadIdx.x; i < nb * dp; i += blockDim.x) {
-      const int j = i / dp, e = i - j * dp;
-      const int64_t t = first + t0 + j;
-      float qv = 0.f, kv = 0.f;
-      if (e < d) {
-        qv = act_apply(A.q[t * A.ldq + (int64_t)g * d + e], A.act);
-        kv = act_apply(A.k[t * A.ldk + (int64_t)g * d + e], A.act);
+    stage_rows(A.q + (int64_t)g * d, A.ldq, first + t0, nb, d, dp, A.act, qs);
+    if (MODE != 2) {
+      stage_rows(A.k + (int64_t)g * d, A.ldk, first + t0, nb, d, dp, A.act, ks);
+      for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
+        const int j = i / kCols, e = i - j * kCols;
+        const int64_t t = first + t0 + j;
+        vs[i] = c0 + e < dv ? act_apply(A.v[t * A.ldv + (int64_t)h * dv + c0 + e], A.act) : 0.f;
       }
-      qs[i] = qv, ks[i] = kv;
-    }
-    for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
-      const int j = i / kCols, e = i - j * kCols;
-      const int64_t t = first + t0 + j;
-      vs[i] = c0 + e < dv ? act_apply(A.v[t * A.ldv + (int64_t)h * dv + c0 + e], A.act) : 0.f;
-    }
-    for (int j = threadIdx.x; j < nb; j += blockDim.x) {
-      const int64_t t = first + t0 + j;
-      ab[2 * j] = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
-      ab[2 * j + 1] = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+      for (int j = threadIdx.x; j < nb; j += blockDim.x) {
+        const int64_t t = first + t0 + j;
+        ab[2 * j] = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
+        ab[2 * j + 1] = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+      }
     }
     __syncthreads();
     for (int j = 0; j < nb; ++j) {
-      const float a = ab[2 * j], bv = ab[2 * j + 1] * vs[j * kCols + lane];
-      const float4* k4 = reinterpret_cast<const float4*>(ks + j * dp + warp * DR);
       const float4* q4 = reinterpret_cast<const float4*>(qs + j * dp + warp * DR);
-      float o = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;   // four chains: the read-out does not wait on one accumulator
+      if (MODE != 2) {
+        const float a = ab[2 * j], bv = ab[2 * j + 1] * vs[j * kCols + lane];
+        const float4* k4 = reinterpret_cast<const float4*>(ks + j * dp + warp * DR);
 #pragma unroll
-      for (int r4 = 0; r4 < DR / 4; ++r4) {
-        const float4 kk = k4[r4], qq = q4[r4];
-        S[4 * r4 + 0] = fmaf(a, S[4 * r4 + 0], kk.x * bv);
-        S[4 * r4 + 1] = fmaf(a, S[4 * r4 + 1], kk.y * bv);
-        S[4 * r4 + 2] = fmaf(a, S[4 * r4 + 2], kk.z * bv);
-        S[4 * r4 + 3] = fmaf(a, S[4 * r4 + 3], kk.w * bv);
-        o = fmaf(S[4 * r4 + 0], qq.x, o);
-        o = fmaf(S[4 * r4 + 1], qq.y, o);
-        o = fmaf(S[4 * r4 + 2], qq.z, o);
-        o = fmaf(S[4 * r4 + 3], qq.w, o);
+        for (int r4 = 0; r4 < DR / 4; ++r4) {
+          const float4 kk = k4[r4], qq = q4[r4];
+          S[4 * r4 + 0] = fmaf(a, S[4 * r4 + 0], kk.x * bv);
+          S[4 * r4 + 1] = fmaf(a, S[4 * r4 + 1], kk.y * bv);
+          S[4 * r4 + 2] = fmaf(a, S[4 * r4 + 2], kk.z * bv);
+          S[4 * r4 + 3] = fmaf(a, S[4 * r4 + 3], kk.w * bv);
+          o0 = fmaf(S[4 * r4 + 0], qq.x, o0);
+          o1 = fmaf(S[4 * r4 + 1], qq.y, o1);
+          o2 = fmaf(S[4 * r4 + 2], qq.z, o2);
+          o3 = fmaf(S[4 * r4 + 3], qq.w, o3);
+        }
+      } else {
+#pragma unroll
+        for (int r4 = 0; r4 < DR / 4; ++r4) {
+          const float4 qq = q4[r4];
+          o0 = fmaf(S[4 * r4 + 0], qq.x, o0);
+          o1 = fmaf(S[4 * r4 + 1], qq.y, o1);
+          o2 = fmaf(S[4 * r4 + 2], qq.z, o2);
+          o3 = fmaf(S[4 * r4 + 3], qq.w, o3);
+        }
       }
-      op[(warp * kTB + j) * kCols + lane] = o;
+      op[(warp * kTB + j) * kCols + lane] = (o0 + o1) + (o2 + o3);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
       const int j = i / kCols, e = i - j * kCols;
       if (c0 + e >= dv) continue;
-      float o = skip * vs[i];
+      float o = 0.f;
       for (int p = 0; p < P; ++p) o += op[(p * kTB + j) * kCols + e];
-      A.out[(int64_t)(first + t0 + j) * A.ld_out + (int64_t)h * dv + c0 + e] = o;
+      float* dst = A.out + (int64_t)(first + t0 + j) * A.ld_out + (int64_t)h * dv + c0 + e;
+      if (MODE == 2)
+        *dst += A.pcum[(int64_t)(first + t0 + j) * A.H + h] * o;
+      else
+        *dst = fmaf(skip, vs[i], o);
     }
   }
-  if (col) {
+  if (MODE != 2 && col) {
 #pragma unroll
     for (int r = 0; r < DR; ++r) {
       const int i = warp * DR + r;
@@ -125,15 +172,52 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256) outer_recurrence_kernel
   }
 }
 
+// Second pass of the tiled form: every element of the state carries on its own through the tiles of its segment,
+// start[k] = S, S = (product of tile k's decays) * S + local[k], from the slot's state (zeros at position 0) to the state
+// the slot keeps.  One thread per (segment, head, element): loads of the next tiles do not wait for the chain.
+__global__ void outer_recurrence_carry_kernel(RecArgs A, const int32_t* __restrict__ tile_first, const int32_t* __restrict__ tile_count) {
+  const int64_t per = (int64_t)A.d * A.dv;
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per) return;
+  const int h = blockIdx.y, seg = blockIdx.z;
+  const int k0 = A.seg_tile0[seg], nk = A.seg_tiles[seg];
+  const int row0 = tile_first[k0];
+  float* st = A.state + ((int64_t)A.slot[row0] * A.H + h) * per + e;
+  float S = A.pos[row0] == 0 ? 0.f : *st;
+  const float* __restrict__ loc = A.ws_local + ((int64_t)k0 * A.H + h) * per + e;
+  float* __restrict__ start = A.ws_start + ((int64_t)k0 * A.H + h) * per + e;
+  const int64_t hop = (int64_t)A.H * per;
+  int k = 0;
+  for (; k + 4 <= nk; k += 4) {
+    float l[4], pe[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      l[u] = loc[(k + u) * hop];
+      pe[u] = A.pcum[(int64_t)(tile_first[k0 + k + u] + tile_count[k0 + k + u] - 1) * A.H + h];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      start[(k + u) * hop] = S;
+      S = fmaf(pe[u], S, l[u]);
+    }
+  }
+  for (; k < nk; ++k) {
+    const float l = loc[k * hop], pe = A.pcum[(int64_t)(tile_first[k0 + k] + tile_count[k0 + k] - 1) * A.H + h];
+    start[k * hop] = S;
+    S = fmaf(pe, S, l);
+  }
+  *st = S;
+}
+
 // rows of the state per warp for a key size: 8 warps up to d = 256, more warps beyond
 inline int rec_rows_per_warp(int d) { return d <= 32 ? 4 : d <= 64 ? 8 : d <= 128 ? 16 : 32; }
 inline size_t rec_smem(int P, int DR) { return ((size_t)kTB * (2 * P * DR + kCols + 2) + (size_t)P * kTB * kCols) * sizeof(float); }
 
-template <int DR>
-int launch_rec(const RecArgs& A, int n_segments, cudaStream_t st) {
+template <int DR, int MODE>
+int launch_rec(const RecArgs& A, int n_ctas, cudaStream_t st) {
   const int P = (A.d + DR - 1) / DR;
   const size_t smem = rec_smem(P, DR);
-  auto kern = outer_recurrence_kernel<DR>;
+  auto kern = outer_recurrence_kernel<DR, MODE>;
   if (smem > 48 * 1024) {
     static bool set = false;   // per instantiation
     if (!set) {
@@ -141,8 +225,18 @@ int launch_rec(const RecArgs& A, int n_segments, cudaStream_t st) {
       set = true;
     }
   }
-  kern<<<dim3((unsigned)n_segments, (unsigned)A.H, (unsigned)((A.dv + kCols - 1) / kCols)), P * 32, smem, st>>>(A);
+  kern<<<dim3((unsigned)n_ctas, (unsigned)A.H, (unsigned)((A.dv + kCols - 1) / kCols)), P * 32, smem, st>>>(A);
   return lm_launch_status();
+}
+
+template <int MODE>
+int launch_rec_mode(const RecArgs& A, int n_ctas, cudaStream_t st) {
+  switch (rec_rows_per_warp(A.d)) {
+    case 4: return launch_rec<4, MODE>(A, n_ctas, st);
+    case 8: return launch_rec<8, MODE>(A, n_ctas, st);
+    case 16: return launch_rec<16, MODE>(A, n_ctas, st);
+    default: return launch_rec<32, MODE>(A, n_ctas, st);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -238,22 +332,34 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy
 
 }  // namespace
 
+extern "C" int64_t ao_lm_outer_recurrence_workspace_bytes(int n_tiles, int64_t n, int H, int d, int dv) {
+  return ((int64_t)2 * n_tiles * H * d * dv + n * H) * 4;
+}
+
 extern "C" int ao_lm_outer_recurrence(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                                       int act, const float* a, const float* b, int64_t ld_ab, const float* a_head,
                                       const float* skip, int H, int G, int d, int dv, float* state, const int32_t* slot,
                                       const int32_t* pos, const int32_t* seg_first, const int32_t* seg_count, int n_segments,
-                                      float* out, int64_t ld_out, void* stream) {
+                                      const int32_t* seg_tile0, const int32_t* seg_tiles, int n_whole_segments, int64_t n,
+                                      float* workspace, float* out, int64_t ld_out, void* stream) {
   LM_CHECK_ARG(q && k && v && state && slot && pos && seg_first && seg_count && out && (a || a_head) && (!b || a));
   LM_CHECK_ARG(n_segments > 0 && H > 0 && G > 0 && H % G == 0 && H <= 65535 && d > 0 && dv > 0 && (act == 0 || act == 1));
   if (d > 1024) return AO_B200_ERR_UNSUPPORTED;
-  RecArgs A{q, k, v, ldq, ldk, ldv, act, a, b, ld_ab, a_head, skip, H, G, d, dv, state, slot, pos, seg_first, seg_count, out, ld_out};
+  RecArgs A{q, k, v, ldq, ldk, ldv, act, a, b, ld_ab, a_head, skip, H, G, d, dv, state, slot, pos, seg_first, seg_count, out, ld_out,
+            nullptr, nullptr, nullptr, seg_tile0, seg_tiles};
   const cudaStream_t st = lm_stream(stream);
-  switch (rec_rows_per_warp(d)) {
-    case 4: return launch_rec<4>(A, n_segments, st);
-    case 8: return launch_rec<8>(A, n_segments, st);
-    case 16: return launch_rec<16>(A, n_segments, st);
-    default: return launch_rec<32>(A, n_segments, st);
-  }
+  if (!seg_tile0) return launch_rec_mode<0>(A, n_segments, st);
+  // tiled form: seg_first / seg_count are tiles, segment s owns tiles seg_tile0[s] .. + seg_tiles[s] - 1
+  LM_CHECK_ARG(seg_tiles && workspace && n_whole_segments > 0 && n_whole_segments <= 65535 && n > 0);
+  const int64_t per = (int64_t)n_segments * H * d * dv;
+  A.ws_local = workspace, A.ws_start = workspace + per, A.pcum = workspace + 2 * per;
+  int rc = launch_rec_mode<1>(A, n_segments, st);
+  if (rc != AO_B200_OK) return rc;
+  outer_recurrence_carry_kernel<<<dim3((unsigned)(((int64_t)d * dv + 255) / 256), (unsigned)H, (unsigned)n_whole_segments), 256, 0, st>>>(
+      A, seg_first, seg_count);
+  rc = lm_launch_status();
+  if (rc != AO_B200_OK) return rc;
+  return launch_rec_mode<2>(A, n_segments, st);
 }
 
 extern "C" int ao_lm_ssd_prep(const float* proj, int64_t ld, int64_t conv_off, int64_t dt_off, int64_t n, int64_t channels,
