@@ -144,32 +144,39 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t ld, int64
 // Every part but x is optional.  The row stays in registers between the two norms (up to kPostPer values per thread).
 constexpr int kPostPer = 8;
 template <typename T, typename TY>
-__global__ void postnorm_residual_kernel(float* __restrict__ x, const TY* __restrict__ y, const T* __restrict__ post_w,
-                                         const float* __restrict__ add_rows, const T* __restrict__ add_vec,
-                                         const T* __restrict__ next_w, float eps, int64_t W, T* __restrict__ h) {
+__global__ void __launch_bounds__(1024) postnorm_residual_kernel(float* __restrict__ x, const TY* __restrict__ y,
+                                                                 const T* __restrict__ post_w, const float* __restrict__ add_rows,
+                                                                 const T* __restrict__ add_vec, const T* __restrict__ next_w,
+                                                                 float eps, int64_t W, T* __restrict__ h) {
   __shared__ float scratch[33];
   const int64_t t = blockIdx.x;
   float* xr = x + t * W;
+  const bool in_regs = W <= (int64_t)kPostPer * blockDim.x;
+  float keep[kPostPer];      // the sublayer's result first, the new residual afterwards
   float k = 0.f;
   if (y) {
     const TY* yr = y + t * W;
     float ss = 0.f;
-    for (int64_t w = threadIdx.x; w < W; w += blockDim.x) {
+#pragma unroll
+    for (int i = 0; i < kPostPer; ++i) {
+      const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
+      keep[i] = w < W ? ldf(yr + w) : 0.f;
+      ss = fmaf(keep[i], keep[i], ss);
+    }
+    for (int64_t w = threadIdx.x + (int64_t)kPostPer * blockDim.x; w < W; w += blockDim.x) {
       const float v = ldf(yr + w);
       ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     k = 1.f / sqrtf(ss / (float)W + eps);
   }
-  const bool in_regs = W <= (int64_t)kPostPer * blockDim.x;
-  float keep[kPostPer];
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < kPostPer; ++i) {
     const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
     if (w < W) {
       float v = xr[w];
-      if (y) v = fmaf(ldf(y + t * W + w) * k, post_w ? ldf(post_w + w) : 1.f, v);
+      if (y) v = fmaf(keep[i] * k, post_w ? ldf(post_w + w) : 1.f, v);
       if (add_rows) v += add_rows[t * W + w];
       if (add_vec) v += ldf(add_vec + w);
       xr[w] = v;
@@ -363,7 +370,8 @@ extern "C" int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const 
                                        const void* add_vec, const void* next_w, int dt, float eps, int64_t n, int64_t width,
                                        void* h, void* stream) {
   LM_CHECK_ARG(x && n > 0 && width > 0 && (!next_w || h) && (y_dt == AO_LM_BF16 || y_dt == AO_LM_F32));
-  const unsigned threads = row_threads(n, width);
+  unsigned threads = row_threads(n, width);
+  while (threads < 1024 && (int64_t)threads * kPostPer < width) threads *= 2;   // the row stays in registers up to 8192 values
   LM_DISPATCH(dt, {
     if (y_dt == AO_LM_F32)
       postnorm_residual_kernel<T, float><<<(unsigned)n, threads, 0, lm_stream(stream)>>>(
