@@ -300,7 +300,7 @@ __global__ void conv_state_save_kernel(const float* __restrict__ x, int64_t ldx,
 // out = norm(y) * weight * sigmoid(gate)              (mode 0: the gate after the norm)
 // out = norm(y * silu(gate)) * weight                 (mode 1: the gate in front of it)
 // with the norm taken over each of `groups` equal parts of the row.  grid (rows, groups).
-constexpr int kNormPer = 8;
+constexpr int kNormPer = 4;
 template <typename T>
 __global__ void __launch_bounds__(1024) gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gate,
                                                                 int64_t ldg, int mode, int64_t width, int groups,
