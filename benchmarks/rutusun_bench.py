@@ -124,7 +124,7 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     # ---- attention of one decoded token over decode_ctx cached keys: the cache rows are read once
     one, last, zero, cnt = i32([0]), i32([decode_ctx]), i32([0]), i32([1])
     o1 = torch.empty(1, H * dv, **bf)
-    ns = max(1, min(-(-C // 32), -(-2 * 148 // G), 64))      # what the step function picks for one sequence
+    ns = max(1, min(-(-C // 32), -(-4 * 148 // G), 64))      # what the step function picks for one sequence
     aws = torch.empty(max(16, int(L.ao_lm_chunk_attention_workspace_bytes(1, G, dv, ns))), dtype=torch.uint8, device=dev)
 
     def attend_decode():

@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ... import _lib
+from ..experts import chosen_experts
 from .model import GLU_ALPHA, Bitipel
 
 # a portion longer than this is cut into pieces (bounds the workspace: the layer results of a step are all kept)
@@ -305,12 +306,8 @@ class StepEngine:
                                                      f.shared_ff, 0, f.shared_limit, GLU_ALPHA, _p(sa), st), "expert_gate_up")
                 _lib.lm_check(L.ao_lm_expert_down(_p(sa), _p(lay.sd), dt, None, None, n, 1, W, f.shared_ff, 0, _p(ffo), st),
                               "expert_down")
-            ya = torch.empty(n * f.top, f.ff, dtype=tdt, device=dev)
-            _lib.lm_check(L.ao_lm_expert_gate_up(_p(xc), _p(lay.wgu), _p(lay.wgu) + f.ff * W * esz, dt, _p(ridx), n, f.top, W, f.ff,
-                                                 2 * f.ff * W, f.limit, GLU_ALPHA, _p(ya), st), "expert_gate_up")
-            _lib.lm_check(L.ao_lm_expert_down(_p(ya), _p(lay.wd), dt, _p(ridx), _p(rwt), n, f.top, W, f.ff, 1 if f.shared_ff else 0,
-                                              _p(ffo), st), "expert_down")
-            return 5 if f.shared_ff else 3
+            return (3 if f.shared_ff else 1) + chosen_experts(L, dt, xc, ridx, rwt, lay.wgu, lay.wd, ffo, f.limit, GLU_ALPHA, 1.0,
+                                                             True, bool(f.shared_ff), st)
         launches = 1
         if f.shared_ff:
             sgu = torch.mm(xc, lay.sgu.t())
@@ -320,42 +317,9 @@ class StepEngine:
             ffo.zero_()
             _lib.lm_check(L.ao_lm_add_cast(_p(sd), dt, n * W, _p(ffo), st), "add_cast")
             launches += 5
-        else:
-            ffo.zero_()
-            launches += 1
-        # rows sorted by expert: one GEMM pair per expert that has rows (the counts come back to the host)
-        flat = ridx.view(-1)
-        order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=f.experts)
-        mrows = n * f.top
-        grouped = tdt == torch.bfloat16 and W % 8 == 0 and f.ff % 8 == 0 and hasattr(torch, "_grouped_mm")
-        if grouped:
-            offs = torch.cumsum(counts, 0).to(torch.int32)
-        else:
-            counts = counts.tolist()   # fp32: one exact library GEMM pair per expert that has rows
-        xs = torch.empty(mrows, W, dtype=tdt, device=dev)
-        _lib.lm_check(L.ao_lm_gather_rows(_p(xc), dt, _p(order), f.top, mrows, W, _p(xs), st), "gather_rows")
-        if grouped:
-            # one grouped GEMM per projection over the sorted rows: the group ends stay on the device
-            gu = torch._grouped_mm(xs, lay.wgu.transpose(1, 2), offs=offs)
-            ya = torch.empty(mrows, f.ff, dtype=tdt, device=dev)
-            _lib.lm_check(L.ao_lm_glu_act(_p(gu), dt, mrows, f.ff, f.limit, GLU_ALPHA, _p(ya), st), "glu_act")
-            ys = torch._grouped_mm(ya, lay.wd.transpose(1, 2), offs=offs)
-            _lib.lm_check(L.ao_lm_scatter_add_rows(_p(ys), dt, _p(order), _p(rwt), f.top, mrows, W, _p(ffo), st), "scatter_add_rows")
-            return launches + 9
-        ys = torch.empty(mrows, W, dtype=tdt, device=dev)
-        ya = torch.empty(max(counts), f.ff, dtype=tdt, device=dev)
-        at = 0
-        for e, c in enumerate(counts):
-            if c == 0:
-                continue
-            gu = torch.mm(xs[at:at + c], lay.wgu[e].t())
-            _lib.lm_check(L.ao_lm_glu_act(_p(gu), dt, c, f.ff, f.limit, GLU_ALPHA, _p(ya), st), "glu_act")
-            torch.mm(ya[:c], lay.wd[e].t(), out=ys[at:at + c])
-            at += c
-            launches += 3
-        _lib.lm_check(L.ao_lm_scatter_add_rows(_p(ys), dt, _p(order), _p(rwt), f.top, mrows, W, _p(ffo), st), "scatter_add_rows")
-        return launches + 4
+        # rows sorted by expert around grouped GEMMs (bf16) or one exact GEMM pair per expert that has rows (fp32)
+        return launches + chosen_experts(L, dt, xc, ridx, rwt, lay.wgu, lay.wd, ffo, f.limit, GLU_ALPHA, 1.0, False,
+                                         bool(f.shared_ff), st)
 
     def _logits(self, x: torch.Tensor, rows: List[int]) -> torch.Tensor:
         """fp32 logits of the given rows: output norm (one number as weight) then the head product with an fp32 result."""

@@ -224,7 +224,7 @@ class SegmentStepEngine:
         key_blocks = -(-chunk // 32)
         if ctas >= self.sm_count or key_blocks <= 2:
             return 1
-        return max(1, min(key_blocks, -(-2 * self.sm_count // ctas), 64))
+        return max(1, min(key_blocks, -(-4 * self.sm_count // ctas), 64))
 
     def _scan_ws(self, meta: StepMeta, channels: int):
         tf, tc, nt, seg0, segn, ns = meta.scan

@@ -300,30 +300,16 @@ __global__ void conv_state_save_kernel(const float* __restrict__ x, int64_t ldx,
 // out = norm(y) * weight * sigmoid(gate)              (mode 0: the gate after the norm)
 // out = norm(y * silu(gate)) * weight                 (mode 1: the gate in front of it)
 // with the norm taken over each of `groups` equal parts of the row.  grid (rows, groups).
-constexpr int kNormPer = 4;
 template <typename T>
-__global__ void __launch_bounds__(1024) gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gate,
-                                                                int64_t ldg, int mode, int64_t width, int groups,
-                                                                const T* __restrict__ weight, float eps, T* __restrict__ out) {
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gate, int64_t ldg,
+                                        int mode, int64_t width, int groups, const T* __restrict__ weight, float eps,
+                                        T* __restrict__ out) {
   __shared__ float scratch[33];
   const int64_t t = blockIdx.x, per = width / groups, c0 = (int64_t)blockIdx.y * per;
   const float* yr = y + t * ldy + c0;
   const float* gr = gate + t * ldg + c0;
-  // mode 0: u = y, f = sigmoid(z) applied after the norm; mode 1: u = y * silu(z), f = 1
-  float u[kNormPer], f[kNormPer];
   float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < kNormPer; ++i) {
-    const int64_t c = threadIdx.x + (int64_t)i * blockDim.x;
-    u[i] = 0.f, f[i] = 1.f;
-    if (c < per) {
-      const float z = gr[c], sg = 1.f / (1.f + expf(-z));
-      u[i] = mode == 1 ? yr[c] * z * sg : yr[c];
-      f[i] = mode == 1 ? 1.f : sg;
-    }
-    ss = fmaf(u[i], u[i], ss);
-  }
-  for (int64_t c = threadIdx.x + (int64_t)kNormPer * blockDim.x; c < per; c += blockDim.x) {
+  for (int64_t c = threadIdx.x; c < per; c += blockDim.x) {
     float v = yr[c];
     if (mode == 1) {
       const float z = gr[c];
@@ -333,15 +319,14 @@ __global__ void __launch_bounds__(1024) gated_group_norm_kernel(const float* __r
   }
   ss = block_sum(ss, scratch);
   const float k = 1.f / sqrtf(ss / (float)per + eps);
-#pragma unroll
-  for (int i = 0; i < kNormPer; ++i) {
-    const int64_t c = threadIdx.x + (int64_t)i * blockDim.x;
-    if (c < per) stf(out + t * width + c0 + c, u[i] * k * ldf(weight + c0 + c) * f[i]);
-  }
-  for (int64_t c = threadIdx.x + (int64_t)kNormPer * blockDim.x; c < per; c += blockDim.x) {
-    const float z = gr[c], sg = 1.f / (1.f + expf(-z));
-    const float v = mode == 1 ? yr[c] * z * sg : yr[c];
-    stf(out + t * width + c0 + c, v * k * ldf(weight + c0 + c) * (mode == 1 ? 1.f : sg));
+  for (int64_t c = threadIdx.x; c < per; c += blockDim.x) {
+    const float z = gr[c];
+    float v = yr[c];
+    if (mode == 1)
+      v = v * (z / (1.f + expf(-z))) * k * ldf(weight + c0 + c);
+    else
+      v = v * k * ldf(weight + c0 + c) / (1.f + expf(-z));
+    stf(out + t * width + c0 + c, v);
   }
 }
 
@@ -402,10 +387,7 @@ extern "C" int ao_lm_gated_group_norm(const float* y, int64_t ldy, const float* 
                                       int64_t width, int groups, const void* weight, int dt, float eps, void* out, void* stream) {
   LM_CHECK_ARG(y && gate && weight && out && n > 0 && width > 0 && groups > 0 && groups <= 65535 && width % groups == 0);
   LM_CHECK_ARG(mode == 0 || mode == 1);
-  const int64_t per = width / groups;
-  unsigned threads = 128;
-  while (threads < 1024 && (int64_t)threads * 4 < per) threads *= 2;
-  LM_DISPATCH(dt, gated_group_norm_kernel<T><<<dim3((unsigned)n, (unsigned)groups), threads, 0, lm_stream(stream)>>>(
+  LM_DISPATCH(dt, gated_group_norm_kernel<T><<<dim3((unsigned)n, (unsigned)groups), 256, 0, lm_stream(stream)>>>(
                       y, ldy, gate, ldg, mode, width, groups, static_cast<const T*>(weight), eps, static_cast<T*>(out)));
   return lm_launch_status();
 }
