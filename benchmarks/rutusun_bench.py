@@ -209,7 +209,7 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     wa, wb_ = torch.ones(W, **bf), torch.ones(W, **bf)
 
     def post():
-        _lib.lm_check(L.ao_lm_postnorm_residual(x.data_ptr(), y.data_ptr(), 1, wa.data_ptr(), None, None, wb_.data_ptr(), 0, 1e-6, n, W,
+        _lib.lm_check(L.ao_lm_postnorm_residual(x.data_ptr(), y.data_ptr(), 1, None, wa.data_ptr(), None, None, wb_.data_ptr(), 0, 1e-6, n, W,
                                                 h.data_ptr(), st), "postnorm_residual")
     ms = timed(post, flush=flush)
     byts = n * W * (4 + 4 + 4 + 2)

@@ -231,22 +231,26 @@ AO_B200_API int ao_lm_ring_append(const void* kn, const void* vn, int64_t n, int
  * duality), sigmoid routers with group-limited choice, SiLU-gated experts.
  */
 
-/* x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * post_w;  x[t] += add_rows[t];  x[t] += add_vec;
+/* y[t] += y_bias (fp32 [width]);  x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * post_w;  x[t] += add_rows[t];  x[t] += add_vec;
  * h[t] = x[t] / sqrt(mean(x[t]^2) + eps) * next_w  (in `dt`).   Every part but x is optional (null): y with post_w (null:
- * ones) is a sublayer's result entering through its own norm, add_rows (fp32 [n][width]) and add_vec (`dt` [width]) are
+ * ones) is a sublayer's result entering through its own norm (y_bias: the bias of the projection that made y, when its GEMM
+ * left it out), add_rows (fp32 [n][width]) and add_vec (`dt` [width]) are
  * what a pass over a looped span of layers adds in front of its first layer, next_w is the next sublayer's input norm. */
-AO_B200_API int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const void* post_w, const float* add_rows,
+AO_B200_API int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const float* y_bias, const void* post_w, const float* add_rows,
                                         const void* add_vec, const void* next_w, int dt, float eps, int64_t n, int64_t width,
                                         void* h, void* stream);
 
 /* ao_lm_qk_prep with what a design may put between the projection and the attention (each optional, null / 0 = none):
  * biases added to the projection (`dt`; q_bias [H d], k_bias [G d], v_bias [G dv]), a weight per coordinate on the
  * unit-RMS queries and keys (`dt` [d], shared by the heads), and a query temperature
- * q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1). */
+ * q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1).  With ring_k / ring_v (a ring of `ring` rows that never wraps: a
+ * full cache) the keys and values also go to row pos[t] of slot[t], which saves the ao_lm_ring_append launch: the attention
+ * reads a step's own rows from kn / vn and only earlier positions from the ring, so the order does not matter there. */
 AO_B200_API int ao_lm_qk_norm_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, const void* q_bias,
                                    const void* k_bias, const void* v_bias, const void* q_weight, const void* k_weight,
-                                   float temp_coef, int temp_every, const int32_t* pos, int64_t n, int H, int G, int d, int dv,
-                                   float eps, int dt, float* qn, void* kn, void* vn, void* stream);
+                                   float temp_coef, int temp_every, const int32_t* pos, const int32_t* slot, void* ring_k,
+                                   void* ring_v, int ring, int64_t n, int H, int G, int d, int dv, float eps, int dt, float* qn,
+                                   void* kn, void* vn, void* stream);
 
 /* ao_lm_chunk_attention / ao_lm_chunk_attention_prompt with gate and dist_bias optional (null) and a sink: exp(sink[head])
  * (fp32 [H]; null: none) joins every row's softmax denominator, without a key or a value and unscaled.  With `chunk` = the

@@ -91,14 +91,17 @@ def test_post_norm_residual_with_pass_additions_and_next_norm(W, parts):
     use_y, use_rows, use_vec, use_next = {"all": (1, 1, 1, 1), "norm_only": (0, 0, 0, 1), "no_next": (1, 1, 0, 0), "vec_only": (0, 0, 1, 1)}[parts]
     ref = x.double()
     if use_y:
-        ref = ref + O.rms_norm(y.double(), pw.double(), eps)
+        ref = ref + O.rms_norm(y.double() + (torch.randn(W, generator=_gen(W + 1)).double() if W != 256 else 0.0), pw.double(), eps)
     if use_rows:
         ref = ref + rows.double()
     if use_vec:
         ref = ref + vec.double()
     xd, yd, rd, pd, vd, nd = x.cuda(), y.cuda(), rows.cuda(), pw.cuda(), vec.cuda(), nw.cuda()
     h = torch.zeros(n, W, device="cuda", dtype=torch.bfloat16)
-    lib.lm_check(L.ao_lm_postnorm_residual(xd.data_ptr(), yd.data_ptr() if use_y else None, lib.DT_F32, pd.data_ptr() if use_y else None,
+    bias = torch.randn(W, generator=_gen(W + 1)) if use_y and W != 256 else None
+    bd = bias.cuda() if bias is not None else None
+    lib.lm_check(L.ao_lm_postnorm_residual(xd.data_ptr(), yd.data_ptr() if use_y else None, lib.DT_F32,
+                                           bd.data_ptr() if bd is not None else None, pd.data_ptr() if use_y else None,
                                            rd.data_ptr() if use_rows else None, vd.data_ptr() if use_vec else None,
                                            nd.data_ptr() if use_next else None, lib.DT_BF16, eps, n, W, h.data_ptr(), _st()), "postnorm")
     assert _close(xd, ref)
@@ -125,13 +128,21 @@ def test_query_key_preparation_bias_weight_and_temperature_steps(H, G, d, dv, ev
     pd, dev = proj.cuda(), [t.cuda() for t in (qb, kb, vb, qw, kw)]
     posd = _i32(pos)
     qn, kn, vn = torch.empty(n, H, d, device="cuda"), torch.empty(n, G, d, device="cuda"), torch.empty(n, G * dv, device="cuda")
+    # positions 0 .. n-1 of slot 1 of a cache with n rows also receive the keys and values
+    ring_k, ring_v = torch.zeros(2, n, G, d, device="cuda"), torch.zeros(2, n, G * dv, device="cuda")
+    rpos, rslot = _i32(list(range(n))[::-1]), _i32([1] * n)
     lib.lm_check(L.ao_lm_qk_norm_prep(pd.data_ptr(), ld, 0, H * d, (H + G) * d, *[t.data_ptr() for t in dev], coef, every,
-                                      posd.data_ptr(), n, H, G, d, dv, eps, lib.DT_F32, qn.data_ptr(), kn.data_ptr(),
-                                      vn.data_ptr(), _st()), "qk_norm_prep")
+                                      posd.data_ptr(), None, None, None, 0, n, H, G, d, dv, eps, lib.DT_F32, qn.data_ptr(),
+                                      kn.data_ptr(), vn.data_ptr(), _st()), "qk_norm_prep")
     assert _close(qn, q_ref) and _close(kn, k_ref) and _close(vn, v_ref)
+    lib.lm_check(L.ao_lm_qk_norm_prep(pd.data_ptr(), ld, 0, H * d, (H + G) * d, *[t.data_ptr() for t in dev], 0.0, 0,
+                                      rpos.data_ptr(), rslot.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), n, n, H, G, d, dv, eps,
+                                      lib.DT_F32, qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), _st()), "qk_norm_prep")
+    assert _close(ring_k[1].flip(0), k_ref) and _close(ring_v[1].flip(0), v_ref) and float(ring_k[0].abs().max()) == 0.0
     # no temperature, no weights, no biases: plain unit-RMS rows
-    lib.lm_check(L.ao_lm_qk_norm_prep(pd.data_ptr(), ld, 0, H * d, (H + G) * d, None, None, None, None, None, 0.0, 0, None, n, H, G, d, dv,
-                                      eps, lib.DT_F32, qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), _st()), "qk_norm_prep")
+    lib.lm_check(L.ao_lm_qk_norm_prep(pd.data_ptr(), ld, 0, H * d, (H + G) * d, None, None, None, None, None, 0.0, 0, None, None, None,
+                                      None, 0, n, H, G, d, dv, eps, lib.DT_F32, qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), _st()),
+                 "qk_norm_prep")
     assert _close(qn, O.unit_rms(proj[:, :H * d].double().view(n, H, d), eps))
 
 
@@ -580,6 +591,26 @@ def test_greedy_generation_through_generator_and_graph(batch):
             assert seq.shape == (batch, 25)
             for b in range(batch):
                 assert seq[b, 13:].tolist() == want, (use_graph, b)
+
+
+def test_sampling_with_temperature_runs_through_the_framework_sampler():
+    from torchao_fork_b200._models.llama.generate import Generator
+    cfg = _plain()
+    m = _model(cfg, O.random_weights(cfg, 27), torch.bfloat16, slots=1)
+    gen = Generator(m, 1, 40, temperature=0.8, top_k=5, use_graph=True)
+    seq = gen.generate(torch.tensor(_tokens(cfg, 6, 6)), 10)
+    assert seq.shape == (1, 16) and int(seq.min()) >= 0 and int(seq.max()) < cfg["vocab"]
+
+
+def test_command_line_generates_from_a_checkpoint_folder_and_a_named_configuration(tmp_path):
+    import importlib
+    G = importlib.import_module("torchao_fork_b200._models.llama.generate")
+    cfg = _mixed()
+    folder = str(tmp_path / "ckpt")
+    O.write_checkpoint(folder, cfg, O.random_weights(cfg, 30))
+    # the calls themselves are the check: folder or name -> registry -> prefill -> graph decode -> sampling
+    G.main(checkpoint_path=folder, num_samples=1, max_new_tokens=9, prompt="1,2,3,4,5", temperature=0.0, precision=torch.float32)
+    G.main(random_init="Rutusun-test", num_samples=1, max_new_tokens=6, prompt="7,8,9")
 
 
 def test_named_configuration_through_the_registry():

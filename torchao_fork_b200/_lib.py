@@ -172,9 +172,9 @@ LM_SIGNATURES = {
     "ao_lm_chunk_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
     "ao_lm_ring_append": [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
-    "ao_lm_postnorm_residual": [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _vp, _vp],
-    "ao_lm_qk_norm_prep": [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _f32,
-                           _i32, _vp, _vp, _vp, _vp],
+    "ao_lm_postnorm_residual": [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _vp, _vp],
+    "ao_lm_qk_norm_prep": [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i32,
+                           _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp],
     "ao_lm_sink_attention": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                              _i32, _i32, _i32, _f32, _f32, _f32, _i32, _vp, _i64, _vp, _i64, _vp],
     "ao_lm_sink_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,

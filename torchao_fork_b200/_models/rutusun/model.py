@@ -21,6 +21,7 @@ l<i>.mlp.{router,correction,e<j>.{gate,up,down},shared.{gate,up,down}}; linear w
 """
 import math
 import os
+import warnings
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
@@ -339,8 +340,8 @@ class Rutusun(nn.Module):
                         L.sgu, L.sd = buf(r + "shared.gu", gu), buf(r + "shared.down", dn)
             self.layers.append(L)
         extra = sorted(set(w) - used)
-        if extra:
-            raise ValueError(f"checkpoint tensors the configuration does not use: {extra[:8]}{' ...' if len(extra) > 8 else ''}")
+        if extra:   # e.g. the feed-forward norms of a layer that has no feed-forward: nothing reads them
+            warnings.warn(f"checkpoint tensors the configuration does not use: {extra[:8]}{' ...' if len(extra) > 8 else ''}")
 
     @classmethod
     def from_checkpoint(cls, folder, device="cuda", dtype=torch.bfloat16):

@@ -6,8 +6,9 @@ The residual x is fp32.  Every sublayer ends in ONE row kernel (`postnorm_residu
 through its own RMS norm, what a pass over the looped span adds in front of its first layer (the embedding output, the
 pass's learned vector) is added, and the next sublayer's input norm is taken while the row is still in registers.
   attention: ONE GEMM [q | k | v] (fp32 result) -> `qk_norm_prep` (biases, weighted unit-RMS queries and keys, query
-      temperature) -> `sink_attention` over the slot's cached keys / values and the step's own rows (tensor-core form
-      for prompt portions in bf16, fp32 form with key splits otherwise) -> `ring_append` -> GEMM W_o (+ bias).
+      temperature; also stores the keys and values in the slot's cache) -> `sink_attention` over the slot's cached keys /
+      values and the step's own rows (tensor-core form for prompt portions in bf16, fp32 form with key splits otherwise)
+      -> GEMM W_o (its bias joins the result in the sublayer's closing kernel).
   lightning: ONE GEMM [q | k | v | gate] (fp32) -> `outer_recurrence` (SiLU on load, fixed decay per head, matrix state
       per slot) -> `gated_group_norm` (norm, then sigmoid gate) -> GEMM W_o.
   mamba2: GEMM W_in (fp32) -> `ssd_prep` (convolution + SiLU over [x | B | C], softplus step sizes, decays) ->
@@ -55,7 +56,7 @@ class StepEngine(SegmentStepEngine):
         return [(la.mixer.heads, la.mixer.kv_heads, la.mixer.dim, la.mixer.vdim, S) for la in self.cfg.layers if la.type == "attention"]
 
     # ------------------------------------------------------------------------------------------------ layers
-    def _post(self, x, y, post_w, enters, emb, next_w, h, st):
+    def _post(self, x, y, post_w, enters, emb, next_w, h, st, y_bias=None):
         """x += norm(y) * post_w; the pass vectors of `enters` (and the embedding output for every pass but the first);
         h = norm(x) * next_w.  One launch unless several passes start at once."""
         m, cfg, L, dt = self.m, self.cfg, self.L, self.dt
@@ -66,11 +67,11 @@ class StepEngine(SegmentStepEngine):
             t = steps.pop(0) if steps else None
             last = not steps
             _lib.lm_check(L.ao_lm_postnorm_residual(
-                _p(x), _p(y), _lib.DT_F32, _p(post_w), _p(emb) if t is not None and t > 0 else None,
+                _p(x), _p(y), _lib.DT_F32, _p(y_bias), _p(post_w), _p(emb) if t is not None and t > 0 else None,
                 m.loop_step[t].data_ptr() if t is not None else None, _p(next_w) if last else None, dt, cfg.norm_eps, n, W,
                 _p(h) if last and next_w is not None else None, st), "postnorm_residual")
             k += 1
-            y = post_w = None
+            y = post_w = y_bias = None
             if last:
                 return k
 
@@ -94,6 +95,7 @@ class StepEngine(SegmentStepEngine):
         for k, (r, li, _) in enumerate(plan):
             lay, rs = m.layers[li], m.run_state[r]
             la = lay.args
+            y_bias = lay.o_b if la.type == "attention" else None     # the output projection's bias joins the result in `_post`
             if la.type == "attention":
                 y, c = self._attention(lay, la.mixer, rs, h, meta, st)
             elif la.type == "lightning":
@@ -106,19 +108,19 @@ class StepEngine(SegmentStepEngine):
             else:
                 nxt_enters, nxt_norm = self.tail_enters, None
             if la.mlp is not None:
-                launches += self._post(x, y, lay.norm1b, [], emb, lay.norm2, h, st)
+                launches += self._post(x, y, lay.norm1b, [], emb, lay.norm2, h, st, y_bias)
                 y, c = self._feed_forward(lay, la.mlp, h, n, st)
                 launches += c
-                post_w = lay.norm2b
+                post_w, y_bias = lay.norm2b, None
             else:
                 post_w = lay.norm1b
             if after_run is not None:       # the residual as the layer leaves it, before the next pass's additions
-                launches += self._post(x, y, post_w, [], emb, None, None, st)
+                launches += self._post(x, y, post_w, [], emb, None, None, st, y_bias)
                 after_run(r, x)
                 if nxt_enters or nxt_norm is not None:
                     launches += self._post(x, None, None, nxt_enters, emb, nxt_norm, h, st)
             else:
-                launches += self._post(x, y, post_w, nxt_enters, emb, nxt_norm, h, st)
+                launches += self._post(x, y, post_w, nxt_enters, emb, nxt_norm, h, st, y_bias)
         self.launches = launches
         return x
 
@@ -150,8 +152,9 @@ class StepEngine(SegmentStepEngine):
         vn = torch.empty(n, G, dv, dtype=tdt, device=dev)
         o = torch.empty(n, H * dv, dtype=tdt, device=dev)
         _lib.lm_check(L.ao_lm_qk_norm_prep(_p(proj), lay.ld, lay.q_off, lay.k_off, lay.v_off, _p(lay.q_b), _p(lay.k_b), _p(lay.v_b),
-                                           _p(lay.q_norm), _p(lay.k_norm), a.temp_coef, a.temp_every, _p(meta.pos), n, H, G, d, dv,
-                                           self.cfg.norm_eps, dt, _p(qn), _p(kn), _p(vn), st), "qk_norm_prep")
+                                           _p(lay.q_norm), _p(lay.k_norm), a.temp_coef, a.temp_every, _p(meta.pos), _p(meta.slot),
+                                           _p(rs.ring.k), _p(rs.ring.v), S, n, H, G, d, dv, self.cfg.norm_eps, dt, _p(qn), _p(kn),
+                                           _p(vn), st), "qk_norm_prep")
         tf, tc, nt, tensor = meta.attn[(H, G, d, dv, S)]
         common = (_p(qn), _p(kn), _p(vn), _p(rs.ring.k), _p(rs.ring.v), dt, None, 0, None, 0, _p(lay.sink), _p(meta.slot),
                   _p(meta.pos), _p(meta.back), _p(tf), _p(tc), nt, H, G, d, dv, S, a.scale, 0.0, 1.0)
@@ -164,11 +167,7 @@ class StepEngine(SegmentStepEngine):
             ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
             _lib.lm_check(L.ao_lm_sink_attention(*common, ns, _p(ws), ws.numel(), _p(o), o.shape[1], st), "sink_attention")
             split = 1 if ns > 1 else 0
-        _lib.lm_check(L.ao_lm_ring_append(_p(kn), _p(vn), n, G * d, G * dv, S, dt, _p(meta.slot), _p(meta.pos), _p(meta.ahead),
-                                          _p(rs.ring.k), _p(rs.ring.v), st), "ring_append")
-        y = self._mm_f32(o, lay.w_out)
-        y.add_(lay.o_b)
-        return y, 6 + split
+        return self._mm_f32(o, lay.w_out), 4 + split
 
     def _lightning(self, lay, a, rs, h, meta: StepMeta, st):
         """Linear attention with a fixed decay per head -> (fp32 [n][W], launches)."""

@@ -51,9 +51,11 @@ template <typename T>
 __global__ void qk_norm_prep_kernel(const float* __restrict__ proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off,
                                     const T* __restrict__ q_bias, const T* __restrict__ k_bias, const T* __restrict__ v_bias,
                                     const T* __restrict__ q_weight, const T* __restrict__ k_weight, float temp_coef,
-                                    int temp_every, const int32_t* __restrict__ pos, int H, int G, int d, int dv, float eps,
-                                    float* __restrict__ qn, T* __restrict__ kn, T* __restrict__ vn) {
+                                    int temp_every, const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                    T* __restrict__ ring_k, T* __restrict__ ring_v, int ring, int H, int G, int d, int dv,
+                                    float eps, float* __restrict__ qn, T* __restrict__ kn, T* __restrict__ vn) {
   const int64_t t = blockIdx.x;
+  const int64_t rrow = ring_k ? (int64_t)slot[t] * ring + pos[t] : 0;     // the row's place in a cache that never wraps
   const float* row = proj + t * ld;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   float temp = 1.f;
@@ -75,11 +77,17 @@ __global__ void qk_norm_prep_kernel(const float* __restrict__ proj, int64_t ld, 
       const float v = (src[c] + (bias ? ldf(bias + off + c) : 0.f)) * k * (wt ? ldf(wt + c) : 1.f);
       if (is_q)
         qn[(t * H + h) * d + c] = v;
-      else
+      else {
         stf(kn + (t * G + (h - H)) * d + c, v);
+        if (ring_k) stf(ring_k + (rrow * G + (h - H)) * d + c, v);
+      }
     }
   }
-  for (int c = threadIdx.x; c < G * dv; c += blockDim.x) stf(vn + t * G * dv + c, row[v_off + c] + (v_bias ? ldf(v_bias + c) : 0.f));
+  for (int c = threadIdx.x; c < G * dv; c += blockDim.x) {
+    const float v = row[v_off + c] + (v_bias ? ldf(v_bias + c) : 0.f);
+    stf(vn + t * G * dv + c, v);
+    if (ring_v) stf(ring_v + rrow * G * dv + c, v);
+  }
 }
 
 template <typename T>
@@ -317,13 +325,16 @@ extern "C" int ao_lm_qk_prep(const float* proj, int64_t ld, int64_t q_off, int64
 
 extern "C" int ao_lm_qk_norm_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, const void* q_bias,
                                   const void* k_bias, const void* v_bias, const void* q_weight, const void* k_weight,
-                                  float temp_coef, int temp_every, const int32_t* pos, int64_t n, int H, int G, int d, int dv,
-                                  float eps, int dt, float* qn, void* kn, void* vn, void* stream) {
+                                  float temp_coef, int temp_every, const int32_t* pos, const int32_t* slot, void* ring_k,
+                                  void* ring_v, int ring, int64_t n, int H, int G, int d, int dv, float eps, int dt, float* qn,
+                                  void* kn, void* vn, void* stream) {
   LM_CHECK_ARG(proj && qn && kn && vn && n > 0 && H > 0 && G > 0 && d > 0 && dv > 0 && (temp_coef == 0.f || (pos && temp_every > 0)));
+  LM_CHECK_ARG((!ring_k && !ring_v) || (ring_k && ring_v && slot && pos && ring > 0));
   LM_DISPATCH(dt, qk_norm_prep_kernel<T><<<(unsigned)n, 128, 0, lm_stream(stream)>>>(
                       proj, ld, q_off, k_off, v_off, static_cast<const T*>(q_bias), static_cast<const T*>(k_bias),
                       static_cast<const T*>(v_bias), static_cast<const T*>(q_weight), static_cast<const T*>(k_weight), temp_coef,
-                      temp_every, pos, H, G, d, dv, eps, qn, static_cast<T*>(kn), static_cast<T*>(vn)));
+                      temp_every, pos, slot, static_cast<T*>(ring_k), static_cast<T*>(ring_v), ring, H, G, d, dv, eps, qn,
+                      static_cast<T*>(kn), static_cast<T*>(vn)));
   return lm_launch_status();
 }
 

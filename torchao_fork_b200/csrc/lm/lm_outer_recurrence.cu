@@ -72,7 +72,7 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_
 // state it ends with goes to ws_local, the running product of its decays to pcum.  MODE 2 (third pass): the read-out of
 // the state the tile starts from (ws_start, made by the carry pass), scaled by the decays up to each row, added to out.
 template <int DR, int MODE>
-__global__ void __launch_bounds__(DR == 32 ? 1024 : 256) outer_recurrence_kernel(RecArgs A) {
+__global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 5) outer_recurrence_kernel(RecArgs A) {
   extern __shared__ __align__(16) float sm[];
   const int P = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int dp = P * DR;                       // d rounded up to what the warps cover

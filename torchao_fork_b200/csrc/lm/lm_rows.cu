@@ -140,12 +140,14 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t ld, int64
 
 // A sublayer's result enters the residual through its own RMS norm (a weight per coordinate), and the next sublayer's
 // input norm is taken in the same pass over the row:
+//   y += y_bias (a projection's bias that its GEMM left out);
 //   x += y / sqrt(mean(y^2) + eps) * post_w;   x += add_rows[t];   x += add_vec;   h = x / sqrt(mean(x^2) + eps) * next_w.
 // Every part but x is optional.  The row stays in registers between the two norms (up to kPostPer values per thread).
 constexpr int kPostPer = 8;
-template <typename T, typename TY>
+template <typename T, typename TY, bool BIAS>
 __global__ void __launch_bounds__(1024) postnorm_residual_kernel(float* __restrict__ x, const TY* __restrict__ y,
-                                                                 const T* __restrict__ post_w, const float* __restrict__ add_rows,
+                                                                 const float* __restrict__ y_bias, const T* __restrict__ post_w,
+                                                                 const float* __restrict__ add_rows,
                                                                  const T* __restrict__ add_vec, const T* __restrict__ next_w,
                                                                  float eps, int64_t W, T* __restrict__ h) {
   __shared__ float scratch[33];
@@ -160,11 +162,11 @@ __global__ void __launch_bounds__(1024) postnorm_residual_kernel(float* __restri
 #pragma unroll
     for (int i = 0; i < kPostPer; ++i) {
       const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
-      keep[i] = w < W ? ldf(yr + w) : 0.f;
+      keep[i] = w < W ? ldf(yr + w) + (BIAS ? y_bias[w] : 0.f) : 0.f;
       ss = fmaf(keep[i], keep[i], ss);
     }
     for (int64_t w = threadIdx.x + (int64_t)kPostPer * blockDim.x; w < W; w += blockDim.x) {
-      const float v = ldf(yr + w);
+      const float v = ldf(yr + w) + (BIAS ? y_bias[w] : 0.f);
       ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
@@ -186,7 +188,7 @@ __global__ void __launch_bounds__(1024) postnorm_residual_kernel(float* __restri
   }
   for (int64_t w = threadIdx.x + (int64_t)kPostPer * blockDim.x; w < W; w += blockDim.x) {
     float v = xr[w];
-    if (y) v = fmaf(ldf(y + t * W + w) * k, post_w ? ldf(post_w + w) : 1.f, v);
+    if (y) v = fmaf((ldf(y + t * W + w) + (BIAS ? y_bias[w] : 0.f)) * k, post_w ? ldf(post_w + w) : 1.f, v);
     if (add_rows) v += add_rows[t * W + w];
     if (add_vec) v += ldf(add_vec + w);
     xr[w] = v;
@@ -366,21 +368,30 @@ extern "C" int ao_lm_glu_act(const void* gu, int dt, int64_t n, int64_t ff, floa
   return ao_lm_glu_act_shift(gu, dt, n, ff, limit, alpha, 1.f, y, stream);
 }
 
-extern "C" int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const void* post_w, const float* add_rows,
+namespace {
+template <typename T, typename TY, bool BIAS>
+void launch_postnorm(float* x, const void* y, const float* y_bias, const void* post_w, const float* add_rows, const void* add_vec,
+                     const void* next_w, float eps, int64_t n, int64_t width, void* h, unsigned threads, void* stream) {
+  postnorm_residual_kernel<T, TY, BIAS><<<(unsigned)n, threads, 0, lm_stream(stream)>>>(
+      x, static_cast<const TY*>(y), y_bias, static_cast<const T*>(post_w), add_rows, static_cast<const T*>(add_vec),
+      static_cast<const T*>(next_w), eps, width, static_cast<T*>(h));
+}
+}  // namespace
+
+extern "C" int ao_lm_postnorm_residual(float* x, const void* y, int y_dt, const float* y_bias, const void* post_w, const float* add_rows,
                                        const void* add_vec, const void* next_w, int dt, float eps, int64_t n, int64_t width,
                                        void* h, void* stream) {
-  LM_CHECK_ARG(x && n > 0 && width > 0 && (!next_w || h) && (y_dt == AO_LM_BF16 || y_dt == AO_LM_F32));
+  LM_CHECK_ARG(x && n > 0 && width > 0 && (!next_w || h) && (y || !y_bias) && (y_dt == AO_LM_BF16 || y_dt == AO_LM_F32));
   unsigned threads = row_threads(n, width);
   while (threads < 1024 && (int64_t)threads * kPostPer < width) threads *= 2;   // the row stays in registers up to 8192 values
   LM_DISPATCH(dt, {
-    if (y_dt == AO_LM_F32)
-      postnorm_residual_kernel<T, float><<<(unsigned)n, threads, 0, lm_stream(stream)>>>(
-          x, static_cast<const float*>(y), static_cast<const T*>(post_w), add_rows, static_cast<const T*>(add_vec),
-          static_cast<const T*>(next_w), eps, width, static_cast<T*>(h));
-    else
-      postnorm_residual_kernel<T, __nv_bfloat16><<<(unsigned)n, threads, 0, lm_stream(stream)>>>(
-          x, static_cast<const __nv_bfloat16*>(y), static_cast<const T*>(post_w), add_rows, static_cast<const T*>(add_vec),
-          static_cast<const T*>(next_w), eps, width, static_cast<T*>(h));
+if (y_dt == AO_LM_F32) {
+      if (y_bias) launch_postnorm<T, float, true>(x, y, y_bias, post_w, add_rows, add_vec, next_w, eps, n, width, h, threads, stream);
+      else launch_postnorm<T, float, false>(x, y, y_bias, post_w, add_rows, add_vec, next_w, eps, n, width, h, threads, stream);
+    } else {
+      if (y_bias) launch_postnorm<T, __nv_bfloat16, true>(x, y, y_bias, post_w, add_rows, add_vec, next_w, eps, n, width, h, threads, stream);
+      else launch_postnorm<T, __nv_bfloat16, false>(x, y, y_bias, post_w, add_rows, add_vec, next_w, eps, n, width, h, threads, stream);
+    }
   });
   return lm_launch_status();
 }
