@@ -250,7 +250,7 @@ def greedy(cfg, w, prompt, n_new):
 
 
 # ------------------------------------------------------------------------------------------------ test models
-def attention_layer(heads=4, kv_heads=2, dim=8, vdim=12, scale=0.4, coef=0.5, every=16, mlp=None):
+def attention_layer(heads=4, kv_heads=2, dim=8, vdim=12, scale=0.4, coef=0.7, every=16, mlp=None):
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
     if coef is not None:
         m["q_temp"] = {"coef": coef, "every": every}
@@ -271,7 +271,7 @@ def dense(ff=40):
     return {"kind": "dense", "ff": ff}
 
 
-def mixture(experts=8, top=2, ff=16, groups=4, keep=2, scale=1.5, shared=24):
+def mixture(experts=8, top=2, ff=16, groups=4, keep=2, scale=2.5, shared=24):
     f = {"kind": "moe", "expert": {"ff": ff},
          "router": {"experts": experts, "top": top, "scale": scale, "groups": {"count": groups, "keep": keep}}}
     if shared:

@@ -378,20 +378,20 @@ def test_gated_group_norm_gate_behind_and_in_front(width, groups):
         assert _close(out, ref), mode
 
 
-@pytest.mark.parametrize("E,groups,keep,top", [(12, 3, 2, 3), (8, 4, 2, 2), (8, 8, 3, 3), (6, 1, 1, 6), (64, 8, 4, 8), (5, 5, 5, 1), (16, 2, 1, 8)])
+@pytest.mark.parametrize("E,groups,keep,top", [(15, 3, 2, 4), (8, 4, 2, 2), (8, 8, 3, 3), (6, 1, 1, 6), (64, 8, 4, 8), (5, 5, 5, 1), (16, 2, 1, 8)])
 def test_router_group_limited_choice_with_negative_scores(E, groups, keep, top):
     lib, L = _lm()
     g, n = _gen(E * 7 + top), 300
     z = torch.randn(n, E, generator=g) * 2
     corr = torch.randn(E, generator=g) * 0.5 - 1.5        # choice scores below zero: a closed group must not win as "0"
-    chosen, weight = O.route(z.double(), corr.double(), groups, keep, top, 1.5)
+    chosen, weight = O.route(z.double(), corr.double(), groups, keep, top, 1.75)
     zd, cd = z.cuda(), corr.cuda()
     idx, wt = torch.empty(n, top, dtype=torch.int32, device="cuda"), torch.empty(n, top, device="cuda")
-    lib.lm_check(L.ao_lm_router_group_topk_logits(zd.data_ptr(), n, E, top, cd.data_ptr(), groups, keep, 1.5, idx.data_ptr(),
+    lib.lm_check(L.ao_lm_router_group_topk_logits(zd.data_ptr(), n, E, top, cd.data_ptr(), groups, keep, 1.75, idx.data_ptr(),
                                                   wt.data_ptr(), _st()), "router")
     assert torch.equal(idx.cpu().long(), chosen)
     assert _close(wt, weight, 1e-6)
-    assert _close(wt.sum(-1), torch.full((n,), 1.5, dtype=F64), 1e-5)
+    assert _close(wt.sum(-1), torch.full((n,), 1.75, dtype=F64), 1e-5)
 
 
 def test_silu_gated_unit_activation():

@@ -111,5 +111,5 @@ def test_oracle_sink_takes_weight_and_router_keeps_groups():
     chosen, weight = O.route(z, torch.full((12,), -2.0, dtype=F64), 3, 1, 2, 2.0)
     assert bool(((chosen // 4)[:, 0] == (chosen // 4)[:, 1]).all())     # both from the one kept group
     assert torch.allclose(weight.sum(-1), torch.full((50,), 2.0, dtype=F64))
-    assert abs(float(O.query_temperature(20, 0.5, 4)[3]) - (1 + 0.5 * math.log(2))) < 1e-12
-    assert float(O.query_temperature(20, 0.5, 4)[2]) == 1.0
+    assert abs(float(O.query_temperature(20, 0.8, 4)[3]) - (1 + 0.8 * math.log(2))) < 1e-12
+    assert float(O.query_temperature(20, 0.8, 4)[2]) == 1.0

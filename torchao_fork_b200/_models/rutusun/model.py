@@ -202,7 +202,7 @@ class RutusunArgs:
 
 def _decays(heads):
     """Per-head decays spread between a short and a long memory."""
-    return [math.exp(-1.0 / (2.0 ** (1 + 7.0 * h / max(1, heads - 1)))) for h in range(heads)]
+    return [1.0 - 2.0 ** -(2.0 + 6.0 * h / max(1, heads - 1)) for h in range(heads)]
 
 
 def _pattern(n_layer, width, heads, kv_heads, dim, ff, vocab, experts=0, top=0, expert_ff=0, state=128, loop=None, kinds=None):
@@ -222,7 +222,7 @@ def _pattern(n_layer, width, heads, kv_heads, dim, ff, vocab, experts=0, top=0, 
         else:
             mlp = MlpArgs("dense", ff)
         layers.append(LayerArgs(kind, mixer, mlp))
-    return RutusunArgs(vocab, width, 1e-6, loop, layers)
+    return RutusunArgs(vocab, width, 1e-5, loop, layers)
 
 
 # named random-init configurations (benchmarks and examples; checkpoints carry their own config.json)

@@ -155,6 +155,12 @@ __global__ void __launch_bounds__(1024) postnorm_residual_kernel(float* __restri
   float* xr = x + t * W;
   const bool in_regs = W <= (int64_t)kPostPer * blockDim.x;
   float keep[kPostPer];      // the sublayer's result first, the new residual afterwards
+  float xk[kPostPer];        // the residual's old values: in flight while the result's norm is reduced
+#pragma unroll
+  for (int i = 0; i < kPostPer; ++i) {
+    const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
+    xk[i] = w < W ? xr[w] : 0.f;
+  }
   float k = 0.f;
   if (y) {
     const TY* yr = y + t * W;
@@ -177,7 +183,7 @@ __global__ void __launch_bounds__(1024) postnorm_residual_kernel(float* __restri
   for (int i = 0; i < kPostPer; ++i) {
     const int64_t w = threadIdx.x + (int64_t)i * blockDim.x;
     if (w < W) {
-      float v = xr[w];
+      float v = xk[i];
       if (y) v = fmaf(keep[i] * k, post_w ? ldf(post_w + w) : 1.f, v);
       if (add_rows) v += add_rows[t * W + w];
       if (add_vec) v += ldf(add_vec + w);
