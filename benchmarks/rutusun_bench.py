@@ -44,7 +44,7 @@ def model_numbers(name, prompt_len, decode_ctx, decode_steps):
         prompt = torch.randint(0, cfg.vocab_size, (1, prompt_len), device=dev)
         pos = torch.arange(prompt_len, device=dev, dtype=torch.int32)
         with torch.no_grad():
-            ms_prefill = timed(lambda: prefill(model, prompt, pos, temperature=0.0, top_k=None), iters=3, warmup=2)
+            ms_prefill = timed(lambda: prefill(model, prompt, pos, temperature=0.0, top_k=None), iters=8, warmup=3)
             prefill(model, prompt[:, :decode_ctx], pos[:decode_ctx], temperature=0.0, top_k=None)
 
             def decode():
