@@ -25,6 +25,9 @@ def test_configuration_round_trip_and_defaults():
     f = a.layers[1].mlp
     assert (f.experts, f.top, f.n_groups, f.keep, f.shared_ff) == (8, 2, 4, 2, 24)
     assert a.layers[0].mixer.conv_channels == 4 * 6 + 2 * 2 * 10
+    one = _cfg()
+    one["layers"][2]["mixer"]["decay"] = 0.875
+    assert RutusunArgs.from_dict(one).layers[2].mixer.decay == [0.875] * 3
     for name, make in rutusun_configs.items():
         b = make()
         assert RutusunArgs.from_dict(b.to_dict()) == b, name

@@ -137,7 +137,9 @@ class RutusunArgs:
                 assert mixer.heads % mixer.kv_heads == 0, f"layer {i}: {mixer.heads} heads over {mixer.kv_heads} key/value heads"
                 assert mixer.temp_coef == 0.0 or mixer.temp_every >= 1, f"layer {i}: {mixer}"
             elif kind == "lightning":
-                mixer = LightningArgs(int(m["heads"]), int(m["dim"]), int(m["vdim"]), [float(v) for v in m["decay"]])
+                dec = m["decay"]
+                dec = [float(v) for v in dec] if isinstance(dec, (list, tuple)) else [float(dec)] * int(m["heads"])   # one number: every head
+                mixer = LightningArgs(int(m["heads"]), int(m["dim"]), int(m["vdim"]), dec)
                 assert len(mixer.decay) == mixer.heads, f"layer {i}: {len(mixer.decay)} decays for {mixer.heads} heads"
             elif kind == "mamba2":
                 mixer = Mamba2Args(int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["conv"]),
