@@ -2,7 +2,9 @@
  * ao_b200_lm.h — C ABI of libao_b200_lm.so: B200 (sm_100a) kernels of the sequence-model mechanisms that are not
  * weight-only linears: fp32 residual stream with scalar-weight RMS norms, token shift, depth-weighted averaging of
  * layer results, latent (compressed key/value) attention with a softmax sink and an output gate, clipped-GLU experts
- * with a softmax top-k router.  Every constant of a mechanism is a parameter.
+ * with a softmax top-k router; residual kept as several streams, gated per-channel recurrences, attention over chunks
+ * with a ring cache; post-norm residual, causal attention with a sink, matrix-state recurrences (decayed linear
+ * attention, state-space duality), sigmoid routers with group-limited choice.  Every constant of a mechanism is a parameter.
  *
  * Same boundary rules as ao_b200.h: device pointers + sizes + cudaStream_t as void*; nothing is allocated, freed,
  * synchronised or retained; every entry point can be captured into a CUDA graph; 0 = ok, else an AO_B200_ERR_* code.

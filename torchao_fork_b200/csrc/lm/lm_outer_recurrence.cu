@@ -12,7 +12,9 @@
 //
 // One CTA = one segment (consecutive rows of one sequence) x one head x 32 value columns.  Lane = column, warp p owns DR
 // rows of the state in registers; tokens are staged 16 at a time in shared memory, each warp leaves its partial read-outs
-// there and the block adds them up once per 16 tokens.
+// there and the block adds them up once per 16 tokens.  A segment longer than a tile runs in three launches instead: every
+// tile from a zero state, the tiles' start states carried through the segment element by element, and the read-out of
+// each tile's start state added to its rows (same sums, another order).
 //
 // Around it: the input side of the state-space mixer (causal convolution over time with the slot's memory + SiLU,
 // softplus step sizes, decays), the convolution memory's update, and the gated group RMS norm both mixers end with.
