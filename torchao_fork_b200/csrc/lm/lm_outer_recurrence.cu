@@ -74,7 +74,7 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_
 // state it ends with goes to ws_local, the running product of its decays to pcum.  MODE 2 (third pass): the read-out of
 // the state the tile starts from (ws_start, made by the carry pass), scaled by the decays up to each row, added to out.
 template <int DR, int MODE>
-__global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 5) outer_recurrence_kernel(RecArgs A) {
+__global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer_recurrence_kernel(RecArgs A) {
   extern __shared__ __align__(16) float sm[];
   const int P = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int dp = P * DR;                       // d rounded up to what the warps cover
@@ -104,24 +104,8 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 5) outer
       A.pcum[(int64_t)(first + j) * A.H + h] = pr;
     }
   }
-  for (int t0 = 0; t0 < count; t0 += kTB) {
-    const int nb = min(kTB, count - t0);
-    __syncthreads();   // the previous round's read-outs are out
-    stage_rows(A.q + (int64_t)g * d, A.ldq, first + t0, nb, d, dp, A.act, qs);
-    if (MODE != 2) {
-      stage_rows(A.k + (int64_t)g * d, A.ldk, first + t0, nb, d, dp, A.act, ks);
-      for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
-        const int j = i / kCols, e = i - j * kCols;
-        const int64_t t = first + t0 + j;
-        vs[i] = c0 + e < dv ? act_apply(A.v[t * A.ldv + (int64_t)h * dv + c0 + e], A.act) : 0.f;
-      }
-      for (int j = threadIdx.x; j < nb; j += blockDim.x) {
-        const int64_t t = first + t0 + j;
-        ab[2 * j] = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
-        ab[2 * j + 1] = A.b ? A.b[t * A.ld_ab + h] : 1.f;
-      }
-    }
-    __syncthreads();
+  // one round = up to kTB staged tokens: every warp folds them into its rows of the state and leaves partial read-outs
+  auto compute_round = [&](int nb) {
     for (int j = 0; j < nb; ++j) {
       const float4* q4 = reinterpret_cast<const float4*>(qs + j * dp + warp * DR);
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;   // four chains: the read-out does not wait on one accumulator
@@ -152,7 +136,8 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 5) outer
       }
       op[(warp * kTB + j) * kCols + lane] = (o0 + o1) + (o2 + o3);
     }
-    __syncthreads();
+  };
+  auto reduce_round = [&](int t0, int nb) {
     for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
       const int j = i / kCols, e = i - j * kCols;
       if (c0 + e >= dv) continue;
@@ -163,6 +148,84 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 5) outer
         *dst += A.pcum[(int64_t)(first + t0 + j) * A.H + h] * o;
       else
         *dst = fmaf(skip, vs[i], o);
+    }
+  };
+  const float* qg = A.q + (int64_t)g * d;
+  const float* kg = A.k + (int64_t)g * d;
+  // Common shapes (8 warps, 16-byte rows): the next round's rows travel from global memory into registers while this
+  // round is computed, so no warp waits for them at the top of a round.
+  const bool piped = DR <= 16 && P == 8 && count > kTB && (d & 3) == 0 && (A.ldq & 3) == 0 && (reinterpret_cast<uintptr_t>(qg) & 15) == 0 &&
+                     (MODE == 2 || ((A.ldk & 3) == 0 && (reinterpret_cast<uintptr_t>(kg) & 15) == 0));
+  if (piped) {
+    float4 rq[2], rk[2];
+    float rv[2], ra = 0.f, rb = 1.f;
+    const int e4 = lane * 4;
+    auto fetch = [&](int t0, int nb) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int j = warp + 8 * r;
+        rq[r] = rk[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < nb && e4 < d) {
+          rq[r] = *reinterpret_cast<const float4*>(qg + (int64_t)(first + t0 + j) * A.ldq + e4);
+          if (MODE != 2) rk[r] = *reinterpret_cast<const float4*>(kg + (int64_t)(first + t0 + j) * A.ldk + e4);
+        }
+        if (MODE != 2) {
+          const int i = threadIdx.x + 256 * r, jv = i / kCols, ev = i - jv * kCols;
+          rv[r] = (jv < nb && c0 + ev < dv) ? A.v[(int64_t)(first + t0 + jv) * A.ldv + (int64_t)h * dv + c0 + ev] : 0.f;
+        }
+      }
+      if (MODE != 2 && (int)threadIdx.x < nb) {
+        const int64_t t = first + t0 + threadIdx.x;
+        ra = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
+        rb = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+      }
+    };
+    auto act4 = [&](float4 x) {
+      x.x = act_apply(x.x, A.act), x.y = act_apply(x.y, A.act), x.z = act_apply(x.z, A.act), x.w = act_apply(x.w, A.act);
+      return x;
+    };
+    fetch(0, min(kTB, count));
+    for (int t0 = 0; t0 < count; t0 += kTB) {
+      const int nb = min(kTB, count - t0);
+      __syncthreads();   // the previous round's read-outs are out
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int j = warp + 8 * r;
+        if (e4 < dp) {
+          *reinterpret_cast<float4*>(qs + j * dp + e4) = act4(rq[r]);
+          if (MODE != 2) *reinterpret_cast<float4*>(ks + j * dp + e4) = act4(rk[r]);
+        }
+        if (MODE != 2) vs[threadIdx.x + 256 * r] = act_apply(rv[r], A.act);
+      }
+      if (MODE != 2 && threadIdx.x < kTB) ab[2 * threadIdx.x] = ra, ab[2 * threadIdx.x + 1] = rb;
+      __syncthreads();
+      if (t0 + kTB < count) fetch(t0 + kTB, min(kTB, count - t0 - kTB));
+      compute_round(nb);
+      __syncthreads();
+      reduce_round(t0, nb);
+    }
+  } else {
+    for (int t0 = 0; t0 < count; t0 += kTB) {
+      const int nb = min(kTB, count - t0);
+      __syncthreads();   // the previous round's read-outs are out
+      stage_rows(qg, A.ldq, first + t0, nb, d, dp, A.act, qs);
+      if (MODE != 2) {
+        stage_rows(kg, A.ldk, first + t0, nb, d, dp, A.act, ks);
+        for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
+          const int j = i / kCols, e = i - j * kCols;
+          const int64_t t = first + t0 + j;
+          vs[i] = c0 + e < dv ? act_apply(A.v[t * A.ldv + (int64_t)h * dv + c0 + e], A.act) : 0.f;
+        }
+        for (int j = threadIdx.x; j < nb; j += blockDim.x) {
+          const int64_t t = first + t0 + j;
+          ab[2 * j] = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
+          ab[2 * j + 1] = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+        }
+      }
+      __syncthreads();
+      compute_round(nb);
+      __syncthreads();
+      reduce_round(t0, nb);
     }
   }
   if (MODE != 2 && col) {
