@@ -10,8 +10,8 @@
 // same instructions whether it arrives alone or inside a prompt portion, so a result does not depend on how the sequence
 // was cut into steps.
 //
-// One CTA = one segment (consecutive rows of one sequence) x one head x 32 value columns.  Lane = column, warp p owns DR
-// rows of the state in registers; tokens are staged 16 at a time in shared memory, each warp leaves its partial read-outs
+// One CTA = one segment (consecutive rows of one sequence) x one head x 32 or 64 value columns.  Lane = one or two
+// columns, warp p owns DR rows of the state in registers; tokens are staged 16 at a time in shared memory, each warp leaves its partial read-outs
 // there and the block adds them up once per 16 tokens.  A segment longer than a tile runs in three launches instead: every
 // tile from a zero state, the tiles' start states carried through the segment element by element, and the read-out of
 // each tile's start state added to its rows (same sums, another order).
@@ -25,7 +25,6 @@ using namespace lm;
 namespace {
 
 constexpr int kTB = 16;        // tokens staged per round
-constexpr int kCols = 32;      // value columns per CTA
 
 __device__ __forceinline__ float act_apply(float v, int act) { return act == 1 ? v / (1.f + expf(-v)) : v; }
 
@@ -73,28 +72,32 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_
 // MODE 0: whole segments on the slots' state.  MODE 1 (tiled form, first pass): a tile of rows from a zero state; the
 // state it ends with goes to ws_local, the running product of its decays to pcum.  MODE 2 (third pass): the read-out of
 // the state the tile starts from (ws_start, made by the carry pass), scaled by the decays up to each row, added to out.
-template <int DR, int MODE>
-__global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer_recurrence_kernel(RecArgs A) {
+template <int DR, int MODE, int NC>   // NC value columns per lane: a CTA covers 32 NC columns
+__global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : (NC == 2 ? 2 : 4)) outer_recurrence_kernel(RecArgs A) {
+  constexpr int KC = 32 * NC;
   extern __shared__ __align__(16) float sm[];
   const int P = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int dp = P * DR;                       // d rounded up to what the warps cover
   float* qs = sm;                              // [kTB][dp]
   float* ks = qs + kTB * dp;                   // [kTB][dp]
-  float* vs = ks + kTB * dp;                   // [kTB][kCols]
-  float* ab = vs + kTB * kCols;                // [kTB][2]
-  float* op = ab + kTB * 2;                    // [P][kTB][kCols]
-  const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kCols, c = c0 + lane;
+  float* vs = ks + kTB * dp;                   // [kTB][KC]
+  float* ab = vs + kTB * KC;                // [kTB][2]
+  float* op = ab + kTB * 2;                    // [P][kTB][KC]
+  const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * KC;
   const int first = A.seg_first[seg], count = A.seg_count[seg];
   const int g = h / (A.H / A.G), d = A.d, dv = A.dv;
-  const bool col = c < dv;
-  float* srow = MODE == 0 ? A.state + (((int64_t)A.slot[first] * A.H + h) * d) * dv + c
-                          : (MODE == 1 ? A.ws_local : A.ws_start) + (((int64_t)seg * A.H + h) * d) * dv + c;
-  float S[DR];
+  float* srow = MODE == 0 ? A.state + (((int64_t)A.slot[first] * A.H + h) * d) * dv
+                          : (MODE == 1 ? A.ws_local : A.ws_start) + (((int64_t)seg * A.H + h) * d) * dv;
+  float S[NC][DR];
   const bool fresh = MODE == 1 || (MODE == 0 && A.pos[first] == 0);
 #pragma unroll
-  for (int r = 0; r < DR; ++r) {
-    const int i = warp * DR + r;
-    S[r] = (!fresh && col && i < d) ? srow[(int64_t)i * dv] : 0.f;
+  for (int cc = 0; cc < NC; ++cc) {
+    const int c = c0 + 32 * cc + lane;
+#pragma unroll
+    for (int r = 0; r < DR; ++r) {
+      const int i = warp * DR + r;
+      S[cc][r] = (!fresh && c < dv && i < d) ? srow[(int64_t)i * dv + c] : 0.f;
+    }
   }
   const float skip = (MODE != 2 && A.skip) ? A.skip[h] : 0.f;
   if (MODE == 1 && blockIdx.z == 0 && threadIdx.x == 0) {   // the decays' running product, once per (tile, head)
@@ -104,61 +107,75 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer
       A.pcum[(int64_t)(first + j) * A.H + h] = pr;
     }
   }
+  const float* qg = A.q + (int64_t)g * d;
+  const float* kg = A.k + (int64_t)g * d;
+  // Common shapes (8 warps, 16-byte rows): the next round's rows travel from global memory into registers while this
+  // round is computed, so no warp waits for them at the top of a round (in the read-out pass: the rows' old results and decay
+  // products as well).
+  const bool piped = DR <= 16 && P == 8 && count > kTB && (d & 3) == 0 && (A.ldq & 3) == 0 && (reinterpret_cast<uintptr_t>(qg) & 15) == 0 &&
+                     (MODE == 2 || ((A.ldk & 3) == 0 && (reinterpret_cast<uintptr_t>(kg) & 15) == 0));
   // one round = up to kTB staged tokens: every warp folds them into its rows of the state and leaves partial read-outs
   auto compute_round = [&](int nb) {
     for (int j = 0; j < nb; ++j) {
       const float4* q4 = reinterpret_cast<const float4*>(qs + j * dp + warp * DR);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;   // four chains: the read-out does not wait on one accumulator
+      float o[NC][4];   // four chains per column: the read-out does not wait on one accumulator
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) o[cc][0] = o[cc][1] = o[cc][2] = o[cc][3] = 0.f;
       if (MODE != 2) {
-        const float a = ab[2 * j], bv = ab[2 * j + 1] * vs[j * kCols + lane];
+        const float a = ab[2 * j];
+        float bv[NC];
+#pragma unroll
+        for (int cc = 0; cc < NC; ++cc) bv[cc] = ab[2 * j + 1] * vs[j * KC + 32 * cc + lane];
         const float4* k4 = reinterpret_cast<const float4*>(ks + j * dp + warp * DR);
 #pragma unroll
         for (int r4 = 0; r4 < DR / 4; ++r4) {
-          const float4 kk = k4[r4], qq = q4[r4];
-          S[4 * r4 + 0] = fmaf(a, S[4 * r4 + 0], kk.x * bv);
-          S[4 * r4 + 1] = fmaf(a, S[4 * r4 + 1], kk.y * bv);
-          S[4 * r4 + 2] = fmaf(a, S[4 * r4 + 2], kk.z * bv);
-          S[4 * r4 + 3] = fmaf(a, S[4 * r4 + 3], kk.w * bv);
-          o0 = fmaf(S[4 * r4 + 0], qq.x, o0);
-          o1 = fmaf(S[4 * r4 + 1], qq.y, o1);
-          o2 = fmaf(S[4 * r4 + 2], qq.z, o2);
-          o3 = fmaf(S[4 * r4 + 3], qq.w, o3);
+          const float4 kk = k4[r4], qq = q4[r4];   // one pair of loads serves every column of the lane
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) {
+            S[cc][4 * r4 + 0] = fmaf(a, S[cc][4 * r4 + 0], kk.x * bv[cc]);
+            S[cc][4 * r4 + 1] = fmaf(a, S[cc][4 * r4 + 1], kk.y * bv[cc]);
+            S[cc][4 * r4 + 2] = fmaf(a, S[cc][4 * r4 + 2], kk.z * bv[cc]);
+            S[cc][4 * r4 + 3] = fmaf(a, S[cc][4 * r4 + 3], kk.w * bv[cc]);
+            o[cc][0] = fmaf(S[cc][4 * r4 + 0], qq.x, o[cc][0]);
+            o[cc][1] = fmaf(S[cc][4 * r4 + 1], qq.y, o[cc][1]);
+            o[cc][2] = fmaf(S[cc][4 * r4 + 2], qq.z, o[cc][2]);
+            o[cc][3] = fmaf(S[cc][4 * r4 + 3], qq.w, o[cc][3]);
+          }
         }
       } else {
 #pragma unroll
         for (int r4 = 0; r4 < DR / 4; ++r4) {
           const float4 qq = q4[r4];
-          o0 = fmaf(S[4 * r4 + 0], qq.x, o0);
-          o1 = fmaf(S[4 * r4 + 1], qq.y, o1);
-          o2 = fmaf(S[4 * r4 + 2], qq.z, o2);
-          o3 = fmaf(S[4 * r4 + 3], qq.w, o3);
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) {
+            o[cc][0] = fmaf(S[cc][4 * r4 + 0], qq.x, o[cc][0]);
+            o[cc][1] = fmaf(S[cc][4 * r4 + 1], qq.y, o[cc][1]);
+            o[cc][2] = fmaf(S[cc][4 * r4 + 2], qq.z, o[cc][2]);
+            o[cc][3] = fmaf(S[cc][4 * r4 + 3], qq.w, o[cc][3]);
+          }
         }
       }
-      op[(warp * kTB + j) * kCols + lane] = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc)
+        op[(warp * kTB + j) * KC + 32 * cc + lane] = (o[cc][0] + o[cc][1]) + (o[cc][2] + o[cc][3]);
     }
   };
   auto reduce_round = [&](int t0, int nb) {
-    for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
-      const int j = i / kCols, e = i - j * kCols;
+    for (int i = threadIdx.x; i < nb * KC; i += blockDim.x) {
+      const int j = i / KC, e = i - j * KC;
       if (c0 + e >= dv) continue;
       float o = 0.f;
-      for (int p = 0; p < P; ++p) o += op[(p * kTB + j) * kCols + e];
+      for (int p = 0; p < P; ++p) o += op[(p * kTB + j) * KC + e];
       float* dst = A.out + (int64_t)(first + t0 + j) * A.ld_out + (int64_t)h * dv + c0 + e;
       if (MODE == 2)
-        *dst += A.pcum[(int64_t)(first + t0 + j) * A.H + h] * o;
+        *dst = piped ? fmaf(ab[2 * j], o, vs[i]) : *dst + A.pcum[(int64_t)(first + t0 + j) * A.H + h] * o;
       else
         *dst = fmaf(skip, vs[i], o);
     }
   };
-  const float* qg = A.q + (int64_t)g * d;
-  const float* kg = A.k + (int64_t)g * d;
-  // Common shapes (8 warps, 16-byte rows): the next round's rows travel from global memory into registers while this
-  // round is computed, so no warp waits for them at the top of a round.
-  const bool piped = DR <= 16 && P == 8 && count > kTB && (d & 3) == 0 && (A.ldq & 3) == 0 && (reinterpret_cast<uintptr_t>(qg) & 15) == 0 &&
-                     (MODE == 2 || ((A.ldk & 3) == 0 && (reinterpret_cast<uintptr_t>(kg) & 15) == 0));
   if (piped) {
     float4 rq[2], rk[2];
-    float rv[2], ra = 0.f, rb = 1.f;
+    float rv[2 * NC], ra = 0.f, rb = 1.f;
     const int e4 = lane * 4;
     auto fetch = [&](int t0, int nb) {
 #pragma unroll
@@ -169,15 +186,21 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer
           rq[r] = *reinterpret_cast<const float4*>(qg + (int64_t)(first + t0 + j) * A.ldq + e4);
           if (MODE != 2) rk[r] = *reinterpret_cast<const float4*>(kg + (int64_t)(first + t0 + j) * A.ldk + e4);
         }
-        if (MODE != 2) {
-          const int i = threadIdx.x + 256 * r, jv = i / kCols, ev = i - jv * kCols;
-          rv[r] = (jv < nb && c0 + ev < dv) ? A.v[(int64_t)(first + t0 + jv) * A.ldv + (int64_t)h * dv + c0 + ev] : 0.f;
-        }
       }
-      if (MODE != 2 && (int)threadIdx.x < nb) {
+#pragma unroll
+      for (int r = 0; r < 2 * NC; ++r) {     // values, or (read-out pass) what the rows hold so far
+        const int i = threadIdx.x + 256 * r, jv = i / KC, ev = i - jv * KC;
+        const float* src = MODE != 2 ? A.v + (int64_t)(first + t0 + jv) * A.ldv : A.out + (int64_t)(first + t0 + jv) * A.ld_out;
+        rv[r] = (jv < nb && c0 + ev < dv) ? src[(int64_t)h * dv + c0 + ev] : 0.f;
+      }
+      if ((int)threadIdx.x < nb) {
         const int64_t t = first + t0 + threadIdx.x;
-        ra = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
-        rb = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+        if (MODE != 2) {
+          ra = A.a ? A.a[t * A.ld_ab + h] : A.a_head[h];
+          rb = A.b ? A.b[t * A.ld_ab + h] : 1.f;
+        } else {
+          ra = A.pcum[t * A.H + h];
+        }
       }
     };
     auto act4 = [&](float4 x) {
@@ -195,9 +218,10 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer
           *reinterpret_cast<float4*>(qs + j * dp + e4) = act4(rq[r]);
           if (MODE != 2) *reinterpret_cast<float4*>(ks + j * dp + e4) = act4(rk[r]);
         }
-        if (MODE != 2) vs[threadIdx.x + 256 * r] = act_apply(rv[r], A.act);
       }
-      if (MODE != 2 && threadIdx.x < kTB) ab[2 * threadIdx.x] = ra, ab[2 * threadIdx.x + 1] = rb;
+#pragma unroll
+      for (int r = 0; r < 2 * NC; ++r) vs[threadIdx.x + 256 * r] = MODE != 2 ? act_apply(rv[r], A.act) : rv[r];
+      if (threadIdx.x < kTB) ab[2 * threadIdx.x] = ra, ab[2 * threadIdx.x + 1] = rb;
       __syncthreads();
       if (t0 + kTB < count) fetch(t0 + kTB, min(kTB, count - t0 - kTB));
       compute_round(nb);
@@ -211,8 +235,8 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer
       stage_rows(qg, A.ldq, first + t0, nb, d, dp, A.act, qs);
       if (MODE != 2) {
         stage_rows(kg, A.ldk, first + t0, nb, d, dp, A.act, ks);
-        for (int i = threadIdx.x; i < nb * kCols; i += blockDim.x) {
-          const int j = i / kCols, e = i - j * kCols;
+        for (int i = threadIdx.x; i < nb * KC; i += blockDim.x) {
+          const int j = i / KC, e = i - j * KC;
           const int64_t t = first + t0 + j;
           vs[i] = c0 + e < dv ? act_apply(A.v[t * A.ldv + (int64_t)h * dv + c0 + e], A.act) : 0.f;
         }
@@ -228,11 +252,15 @@ __global__ void __launch_bounds__(DR == 32 ? 1024 : 256, DR == 32 ? 1 : 4) outer
       reduce_round(t0, nb);
     }
   }
-  if (MODE != 2 && col) {
+  if (MODE != 2) {
 #pragma unroll
-    for (int r = 0; r < DR; ++r) {
-      const int i = warp * DR + r;
-      if (i < d) srow[(int64_t)i * dv] = S[r];
+    for (int cc = 0; cc < NC; ++cc) {
+      const int c = c0 + 32 * cc + lane;
+#pragma unroll
+      for (int r = 0; r < DR; ++r) {
+        const int i = warp * DR + r;
+        if (c < dv && i < d) srow[(int64_t)i * dv + c] = S[cc][r];
+      }
     }
   }
 }
@@ -276,13 +304,14 @@ __global__ void outer_recurrence_carry_kernel(RecArgs A, const int32_t* __restri
 
 // rows of the state per warp for a key size: 8 warps up to d = 256, more warps beyond
 inline int rec_rows_per_warp(int d) { return d <= 32 ? 4 : d <= 64 ? 8 : d <= 128 ? 16 : 32; }
-inline size_t rec_smem(int P, int DR) { return ((size_t)kTB * (2 * P * DR + kCols + 2) + (size_t)P * kTB * kCols) * sizeof(float); }
+inline size_t rec_smem(int P, int DR, int KC) { return ((size_t)kTB * (2 * P * DR + KC + 2) + (size_t)P * kTB * KC) * sizeof(float); }
 
-template <int DR, int MODE>
+template <int DR, int MODE, int NC>
 int launch_rec(const RecArgs& A, int n_ctas, cudaStream_t st) {
+  constexpr int KC = 32 * NC;
   const int P = (A.d + DR - 1) / DR;
-  const size_t smem = rec_smem(P, DR);
-  auto kern = outer_recurrence_kernel<DR, MODE>;
+  const size_t smem = rec_smem(P, DR, KC);
+  auto kern = outer_recurrence_kernel<DR, MODE, NC>;
   if (smem > 48 * 1024) {
     static bool set = false;   // per instantiation
     if (!set) {
@@ -290,17 +319,20 @@ int launch_rec(const RecArgs& A, int n_ctas, cudaStream_t st) {
       set = true;
     }
   }
-  kern<<<dim3((unsigned)n_ctas, (unsigned)A.H, (unsigned)((A.dv + kCols - 1) / kCols)), P * 32, smem, st>>>(A);
+  kern<<<dim3((unsigned)n_ctas, (unsigned)A.H, (unsigned)((A.dv + KC - 1) / KC)), P * 32, smem, st>>>(A);
   return lm_launch_status();
 }
 
+// two value columns per lane when the value size fills them (one pair of key / query loads then serves both); key sizes
+// above 128 keep one column: their 32 rows per warp fill the registers
 template <int MODE>
 int launch_rec_mode(const RecArgs& A, int n_ctas, cudaStream_t st) {
+  const bool two = A.dv > 32;
   switch (rec_rows_per_warp(A.d)) {
-    case 4: return launch_rec<4, MODE>(A, n_ctas, st);
-    case 8: return launch_rec<8, MODE>(A, n_ctas, st);
-    case 16: return launch_rec<16, MODE>(A, n_ctas, st);
-    default: return launch_rec<32, MODE>(A, n_ctas, st);
+    case 4: return two ? launch_rec<4, MODE, 2>(A, n_ctas, st) : launch_rec<4, MODE, 1>(A, n_ctas, st);
+    case 8: return two ? launch_rec<8, MODE, 2>(A, n_ctas, st) : launch_rec<8, MODE, 1>(A, n_ctas, st);
+    case 16: return two ? launch_rec<16, MODE, 2>(A, n_ctas, st) : launch_rec<16, MODE, 1>(A, n_ctas, st);
+    default: return launch_rec<32, MODE, 1>(A, n_ctas, st);
   }
 }
 
