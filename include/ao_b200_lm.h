@@ -303,7 +303,8 @@ AO_B200_API int ao_lm_conv_state_save(const float* x, int64_t ldx, int64_t n, in
                                       void* stream);
 
 /* RMS norm over each of `groups` equal parts of a row, with a gate:  mode 0: out = norm(y) * weight * sigmoid(gate);
- * mode 1: out = norm(y * silu(gate)) * weight.  y, gate fp32 with row strides; out [n][width] in `dt`. */
+ * mode 1: out = norm(y * silu(gate)) * weight;  mode 2: out = norm(y) * weight * silu(gate).  weight == null: ones.
+ * y, gate fp32 with row strides; out [n][width] in `dt`. */
 AO_B200_API int ao_lm_gated_group_norm(const float* y, int64_t ldy, const float* gate, int64_t ldg, int mode, int64_t n,
                                        int64_t width, int groups, const void* weight, int dt, float eps, void* out,
                                        void* stream);
@@ -322,6 +323,92 @@ AO_B200_API int ao_lm_glu_act_shift(const void* gu, int dt, int64_t n, int64_t f
 AO_B200_API int ao_lm_expert_gate_up_shift(const void* h, const void* w_gate, const void* w_up, int dt, const int32_t* idx,
                                            int64_t n, int top, int64_t width, int64_t ff, int64_t expert_stride, float limit,
                                            float alpha, float shift, void* y, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Layer-norm residual, rotary positions on a projection, time mixing with a decay per key channel, attention under a
+ * sliding window that keeps the first tokens (with several maps per head), routers that renormalise over the chosen
+ * experts, experts without a gate.
+ */
+
+/* x[r] += mult * y[r] (y fp32 [n][width]; null: nothing is added);  out[i] = (x[r] - mean) / sqrt(var + eps) * weight + bias
+ * with var the mean of the squared deviations (weight null: no norm, only the add; bias null: none), r = rows ? rows[i] : i
+ * (rows only without y).  The result is written as fp32 (out_f32) and / or in `dt` (out), [m][width]. */
+AO_B200_API int ao_lm_add_layer_norm(float* x, const float* y, float mult, const int32_t* rows, int64_t m, int64_t width,
+                                     const void* weight, const void* bias, int dt, float eps, float* out_f32, void* out,
+                                     void* stream);
+
+/* Rotary positions, in place, on two blocks of an fp32 projection row (block a: heads_a heads of d at off_a, block b
+ * likewise; a block of 0 heads is skipped): the first rot_dims coordinates of every head turn by pos * inv_freq[i]
+ * (fp32 [rot_dims / 2]); pairing 0 couples (2i, 2i + 1), pairing 1 couples (i, i + rot_dims / 2); then the whole head is
+ * multiplied by the block's scale. */
+AO_B200_API int ao_lm_rotary_rows(float* proj, int64_t ld, int64_t n, const int32_t* pos, const float* inv_freq, int rot_dims,
+                                  int pairing, int d, int64_t off_a, int heads_a, float scale_a, int64_t off_b, int heads_b,
+                                  float scale_b, void* stream);
+
+/* mixes[s][t][:] = h[t] + (prev - h[t]) * mu[s][:] for s < n_mix (mu: `dt` [n_mix][width], mixes: `dt` [n_mix][n][width]);
+ * prev = h[t - 1] when back[t] > 0, the slot's saved row state[slot[t]] when the segment continues an earlier step, zeros
+ * at position 0.  The state is written by the recurrence that ends the layer (ao_lm_channel_recurrence). */
+AO_B200_API int ao_lm_token_shift_mix(const float* h, const void* mu, int n_mix, int dt, const float* state, const int32_t* slot,
+                                      const int32_t* pos, const int32_t* back, int64_t n, int64_t width, void* mixes,
+                                      void* stream);
+
+/* out[t][c] = f(in[t][c]) * row_scale[t * ld_scale] (row_scale null: 1); kind 0: relu(z)^2, kind 1: tanh(z), kind 2:
+ * param * tanh(z / param) (a soft cap).  (in_dt, out_dt): (F32, F32), (F32, BF16) or (BF16, BF16); out may be in. */
+AO_B200_API int ao_lm_unary_rows(const void* in, int in_dt, int64_t n, int64_t cols, int kind, float param, const float* row_scale,
+                                 int64_t ld_scale, void* out, int out_dt, void* stream);
+
+/* Matrix-state recurrence with a decay per key channel and a bonus for the current token, per head (S: d x dv, fp32
+ * state[slots][H][d][dv], zeros at position 0):
+ *   out[t][h] = (S_(t-1) + diag(bonus_h) k_t v_t^T)^T r_t,     S_t = diag(w_t) S_(t-1) + k_t v_t^T.
+ * r, k, w rows hold H heads of d, v rows H heads of dv (fp32).  w_bias (`dt` [H d]) non-null: the decay is made on load
+ * from its pre-activation, w = exp(-exp(w + w_bias)).  bonus: `dt` [H d] or null.  d <= 128.
+ * Segments and the tiled form as in ao_lm_outer_recurrence (workspace from ao_lm_channel_recurrence_workspace_bytes).
+ * With shift_state, the last row of every segment of shift_src (fp32 [n][shift_width]) becomes shift_state[slot]: the
+ * memory of the token shift that made this layer's inputs. */
+AO_B200_API int64_t ao_lm_channel_recurrence_workspace_bytes(int n_tiles, int64_t n, int H, int d, int dv);
+AO_B200_API int ao_lm_channel_recurrence(const float* r, int64_t ldr, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                                         const float* w, int64_t ldw, const void* w_bias, const void* bonus, int dt, int H, int d,
+                                         int dv, float* state, const int32_t* slot, const int32_t* pos, const int32_t* seg_first,
+                                         const int32_t* seg_count, int n_segments, const int32_t* seg_tile0,
+                                         const int32_t* seg_tiles, int n_whole_segments, int64_t n, float* workspace,
+                                         const float* shift_src, float* shift_state, int64_t shift_width, float* out,
+                                         int64_t ld_out, void* stream);
+
+/* Attention under a sliding window that keeps the first tokens: the query at position i sees key j when j <= i and
+ * (i - j < window or j < keep).  n_maps (1 or 2) attention maps per head with queries and keys of their own over the same
+ * values: qn fp32 [n][H][n_maps][d], keys `dt` [..][G][n_maps][d], values `dt` [..][G][dv]; two maps give
+ * a_1 - lambda * a_2.  unit_rms != 0 divides the result by sqrt(mean over dv of its squares + eps); then times out_scale.
+ * ao_lm_qkv_rotary_prep: projection row (fp32) -> biases (`dt`, null: none), rotation (as ao_lm_rotary_rows) of q_heads
+ * query heads and k_heads key heads of d, values copied; k_heads == 0: queries only.
+ * Keys of earlier steps: position p in row p % ring of ring_k / ring_v [slots][ring][...] (ring >= window), and the first
+ * first_rows (>= keep) positions in first_k / first_v [slots][first_rows][...]; the step's own rows from kn / vn.
+ * ao_lm_window_append stores the step's rows, after the last layer that reads the cache has run.
+ * tile_first / tile_count: runs of <= tile_rows consecutive rows of one segment (ao_lm_window_attention_plan; 0 = shape not
+ * covered). */
+AO_B200_API int ao_lm_qkv_rotary_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off,
+                                      const void* q_bias, const void* k_bias, const void* v_bias, const int32_t* pos,
+                                      const float* inv_freq, int rot_dims, int pairing, int64_t n, int q_heads, int k_heads, int d,
+                                      int v_width, int dt, float* qn, void* kn, void* vn, void* stream);
+AO_B200_API int ao_lm_window_append(const void* kn, const void* vn, int64_t n, int64_t k_row, int64_t v_row, int ring,
+                                    int first_rows, int dt, const int32_t* slot, const int32_t* pos, const int32_t* ahead,
+                                    void* ring_k, void* ring_v, void* first_k, void* first_v, void* stream);
+AO_B200_API int ao_lm_window_attention_plan(int dt, int n_maps, int H, int G, int d, int dv, int* tile_rows);
+AO_B200_API int ao_lm_window_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
+                                       const void* first_k, const void* first_v, int ring, int first_rows, int dt,
+                                       const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
+                                       const int32_t* tile_count, int n_tiles, int n_maps, int H, int G, int d, int dv,
+                                       int window, int keep, float scale, float lambda, int unit_rms, float eps, float out_scale,
+                                       void* out, int64_t ld_out, void* stream);
+
+/* Router over fp32 logits[n][ld] (+ bias, fp32 [E], null: none): the `top` largest logits (ties: lowest index) ->
+ * idx[t][top], weight = softmax over the chosen logits only.  extra >= 0: extra_out[t] = sigmoid(logits[t][extra]), a gate
+ * whose logit the same GEMM made. */
+AO_B200_API int ao_lm_router_topk_renorm_logits(const float* logits, int64_t ld, const float* bias, int64_t n, int E, int top,
+                                                int extra, int32_t* idx, float* weight, float* extra_out, void* stream);
+
+/* ao_lm_expert_gate_up for experts without a gate: y[p][ff] = act(w_up[e] h[t]); act 0: relu(.)^2. */
+AO_B200_API int ao_lm_expert_up_act(const void* h, const void* w_up, int dt, const int32_t* idx, int64_t n, int top, int64_t width,
+                                    int64_t ff, int64_t expert_stride, int act, void* y, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,7 @@
 """Per-sequence memory of the models: key/value caches of the gpt-fast Llama (plain and int8), and the state of
 sequence models that keep something else per request — compressed (latent) keys, the previous token's input of a
-token-shift layer, a ring of keys and values for attention that never looks past a fixed span, the state of a
+token-shift layer, a ring of keys and values for attention that never looks past a fixed span (with a small store beside it for
+first tokens that stay visible for good), the state of a
 recurrence (a vector or a matrix per head), the last inputs of a short convolution — in numbered slots that a host-side allocator hands out and takes
 back.
 """
@@ -141,6 +142,27 @@ class RingKVCache(nn.Module):
 
     def grow(self, n_slots):
         self.k, self.v = _grown(self.k, n_slots), _grown(self.v, n_slots)
+
+
+class WindowKVCache(nn.Module):
+    """Keys and values of an attention whose mask is a sliding window plus the first tokens of the sequence: a ring of
+    `ring` rows (>= the widest window of the layers that read it; position p in row p % ring) and, beside it, the first
+    `first_rows` positions (>= the most first tokens that any reader keeps), which the ring's turning never reaches.
+    k_width / v_width are whole rows (all key/value heads, all attention maps of a head).  What a sequence costs does not
+    grow with its length."""
+
+    def __init__(self, n_slots, ring, first_rows, k_width, v_width, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        assert ring > 0 and first_rows >= 0
+        self.ring, self.first_rows = ring, first_rows
+        self.register_buffer("k", torch.zeros(n_slots, ring, k_width, dtype=dtype, device=device))
+        self.register_buffer("v", torch.zeros(n_slots, ring, v_width, dtype=dtype, device=device))
+        self.register_buffer("k_first", torch.zeros(n_slots, max(1, first_rows), k_width, dtype=dtype, device=device))
+        self.register_buffer("v_first", torch.zeros(n_slots, max(1, first_rows), v_width, dtype=dtype, device=device))
+
+    def grow(self, n_slots):
+        self.k, self.v = _grown(self.k, n_slots), _grown(self.v, n_slots)
+        self.k_first, self.v_first = _grown(self.k_first, n_slots), _grown(self.v_first, n_slots)
 
 
 class RecurrentState(nn.Module):

@@ -45,6 +45,9 @@ def _load_builtin():
     from .rutusun import model as _rutusun
     register(Family("rutusun", from_folder=_rutusun.Rutusun.from_checkpoint, from_name=_rutusun.Rutusun.from_name,
                     names=lambda: list(_rutusun.rutusun_configs)))
+    from .fedipel import model as _fedipel
+    register(Family("fedipel", from_folder=_fedipel.Fedipel.from_checkpoint, from_name=_fedipel.Fedipel.from_name,
+                    names=lambda: list(_fedipel.fedipel_configs)))
 
 
 def architecture_of(folder) -> str:

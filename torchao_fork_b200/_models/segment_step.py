@@ -100,19 +100,25 @@ class SegmentStepEngine:
         # rows of one sequence that an attention CTA takes, per attention shape (H, G, d, dv, chunk) of the model
         self.attn_keys, self.prompt_keys = {}, {}
         for shape in self._attention_shapes():
-            H, G, d, dv, chunk = shape
-            tr = ctypes.c_int()
-            _lib.lm_check(self.L.ao_lm_chunk_attention_plan(self.dt, H, G, d, dv, ctypes.byref(tr)), "chunk_attention_plan")
-            if tr.value <= 0:
+            rows, chunk, prompt_rows = self._attention_plan(shape)
+            if rows <= 0:
                 raise NotImplementedError(f"attention shape not covered by the kernels: {shape}")
-            self.attn_keys[shape] = (tr.value, chunk, False)
-            _lib.lm_check(self.L.ao_lm_chunk_attention_prompt_plan(self.dt, H, G, d, dv, ctypes.byref(tr)), "chunk_attention_prompt_plan")
-            if tr.value > 0:
-                self.prompt_keys[shape] = (tr.value, chunk, True)
+            self.attn_keys[shape] = (rows, chunk, False)
+            if prompt_rows > 0:
+                self.prompt_keys[shape] = (prompt_rows, chunk, True)
 
     def _attention_shapes(self):
-        """(H, G, d, dv, chunk) of every attention layer of the model."""
+        """One hashable shape per kind of attention layer of the model; (H, G, d, dv, chunk) for the chunk kernels."""
         return []
+
+    def _attention_plan(self, shape):
+        """-> (rows of one sequence that an attention CTA takes, span of positions that a tile must not leave, rows per
+        CTA of the tensor-core form for prompt portions or 0).  A family whose attention is another kernel overrides it."""
+        H, G, d, dv, chunk = shape
+        tr, pr = ctypes.c_int(), ctypes.c_int()
+        _lib.lm_check(self.L.ao_lm_chunk_attention_plan(self.dt, H, G, d, dv, ctypes.byref(tr)), "chunk_attention_plan")
+        _lib.lm_check(self.L.ao_lm_chunk_attention_prompt_plan(self.dt, H, G, d, dv, ctypes.byref(pr)), "chunk_attention_prompt_plan")
+        return tr.value, chunk, pr.value
 
     # ------------------------------------------------------------------------------------------------ public
     @torch.no_grad()

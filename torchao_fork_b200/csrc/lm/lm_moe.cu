@@ -272,6 +272,68 @@ __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict_
   if (lane == 0) out[t * W + w] = (accumulate ? out[t * W + w] : 0.f) + acc;
 }
 
+// Top-k on the raw logits, weights = softmax over the chosen logits only.  One warp per token over fp32 logits[n][ld] that
+// a GEMM has made; bias (fp32 [E]; null: none) is added first.  Column `extra` of the same row (>= 0) is a gate logit that
+// rode along in the GEMM: extra_out[t] = sigmoid(logits[t][extra]).
+__global__ void router_topk_renorm_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ bias, int64_t n,
+                                          int E, int top, int extra, int32_t* __restrict__ idx, float* __restrict__ weight,
+                                          float* __restrict__ extra_out) {
+  extern __shared__ float sm[];   // [kWarps][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * kWarps + warp;
+  if (t >= n) return;
+  float* z = sm + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[t * ld + e] + (bias ? bias[e] : 0.f);
+  if (extra >= 0 && lane == 0) extra_out[t] = 1.f / (1.f + expf(-logits[t * ld + extra]));
+  __syncwarp();
+  float first = 0.f, den = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = E;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] > best) best = z[e], at = e;          // ascending e: the lowest index wins inside a lane
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
+    }
+    if (k == 0) first = best;                        // the largest logit: the softmax's reference point
+    const float p = expf(best - first);
+    den += p;
+    if (lane == 0) {
+      idx[t * top + k] = at;
+      weight[t * top + k] = p;                       // divided by the sum below
+      if (at < E) z[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  for (int j = lane; j < top; j += 32) weight[t * top + j] /= den;
+}
+
+// grid (ceil(ff / 8), pairs): a warp computes one row of the up projection of its pair's expert; the unit has no gate:
+// y = act(w_up[e] h), act 0: the square of relu.
+template <typename T>
+__global__ void expert_up_act_kernel(const T* __restrict__ h, const T* __restrict__ wu, const int32_t* __restrict__ idx, int top,
+                                     int64_t W, int64_t ff, int64_t expert_stride, int act, T* __restrict__ y) {
+  extern __shared__ float xs[];   // [W]
+  const int64_t p = blockIdx.y, t = p / top;
+  const int64_t e = idx ? idx[p] : 0;
+  stage_f32(h + t * W, xs, W);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t f = (int64_t)blockIdx.x * kWarps + warp;
+  if (f >= ff) return;
+  const bool vec = rows_vectorizable<T>(wu, W) && (expert_stride % (16 / (int)sizeof(T)) == 0);
+  const float a = warp_dot(wu + e * expert_stride + f * W, xs, W, lane, vec);
+  if (lane == 0) {
+    T ra;
+    stf(&ra, a);                  // the projection's output is an activation of the storage type: round it as a GEMM would
+    const float r = fmaxf(ldf(&ra), 0.f);
+    (void)act;
+    stf(y + p * ff + f, r * r);
+  }
+}
+
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ h, const int64_t* __restrict__ src, int top, int64_t W, T* __restrict__ xs) {
   const int64_t i = blockIdx.x, t = src[i] / top;
@@ -356,6 +418,31 @@ extern "C" int ao_lm_expert_down(const void* y, const void* w_down, int dt, cons
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     kern<<<grid, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(y), static_cast<const T*>(w_down), idx, weight, top,
                                                         width, ff, accumulate, out);
+  });
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_router_topk_renorm_logits(const float* logits, int64_t ld, const float* bias, int64_t n, int E, int top,
+                                               int extra, int32_t* idx, float* weight, float* extra_out, void* stream) {
+  LM_CHECK_ARG(logits && idx && weight && n > 0 && E > 0 && top > 0 && top <= E && ld >= E && (extra < 0 || (extra < ld && extra_out)));
+  const size_t smem = (size_t)kWarps * E * sizeof(float);
+  if (smem > 48 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  router_topk_renorm_kernel<<<(unsigned)((n + kWarps - 1) / kWarps), kWarps * 32, smem, lm_stream(stream)>>>(
+      logits, ld, bias, n, E, top, extra, idx, weight, extra_out);
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_expert_up_act(const void* h, const void* w_up, int dt, const int32_t* idx, int64_t n, int top, int64_t width,
+                                   int64_t ff, int64_t expert_stride, int act, void* y, void* stream) {
+  LM_CHECK_ARG(h && w_up && y && n > 0 && top > 0 && width > 0 && ff > 0 && n * top <= 65535 && act == 0);
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((ff + kWarps - 1) / kWarps), (unsigned)(n * top));
+  LM_DISPATCH(dt, {
+    auto kern = expert_up_act_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    kern<<<grid, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_up), idx, top, width, ff,
+                                                        expert_stride, act, static_cast<T*>(y));
   });
   return lm_launch_status();
 }

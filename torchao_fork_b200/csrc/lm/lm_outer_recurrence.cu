@@ -396,6 +396,7 @@ __global__ void conv_state_save_kernel(const float* __restrict__ x, int64_t ldx,
 
 // out = norm(y) * weight * sigmoid(gate)              (mode 0: the gate after the norm)
 // out = norm(y * silu(gate)) * weight                 (mode 1: the gate in front of it)
+// out = norm(y) * weight * silu(gate)                 (mode 2; weight == null: ones)
 // with the norm taken over each of `groups` equal parts of the row.  grid (rows, groups).
 template <typename T>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gate, int64_t ldg,
@@ -419,10 +420,13 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy
   for (int64_t c = threadIdx.x; c < per; c += blockDim.x) {
     const float z = gr[c];
     float v = yr[c];
+    const float wt = weight ? ldf(weight + c0 + c) : 1.f;
     if (mode == 1)
-      v = v * (z / (1.f + expf(-z))) * k * ldf(weight + c0 + c);
+      v = v * (z / (1.f + expf(-z))) * k * wt;
+    else if (mode == 2)
+      v = v * k * wt * (z / (1.f + expf(-z)));
     else
-      v = v * k * ldf(weight + c0 + c) / (1.f + expf(-z));
+      v = v * k * wt / (1.f + expf(-z));
     stf(out + t * width + c0 + c, v);
   }
 }
@@ -482,8 +486,8 @@ extern "C" int ao_lm_conv_state_save(const float* x, int64_t ldx, int64_t n, int
 
 extern "C" int ao_lm_gated_group_norm(const float* y, int64_t ldy, const float* gate, int64_t ldg, int mode, int64_t n,
                                       int64_t width, int groups, const void* weight, int dt, float eps, void* out, void* stream) {
-  LM_CHECK_ARG(y && gate && weight && out && n > 0 && width > 0 && groups > 0 && groups <= 65535 && width % groups == 0);
-  LM_CHECK_ARG(mode == 0 || mode == 1);
+  LM_CHECK_ARG(y && gate && out && n > 0 && width > 0 && groups > 0 && groups <= 65535 && width % groups == 0);
+  LM_CHECK_ARG(mode == 0 || mode == 1 || mode == 2);
   LM_DISPATCH(dt, gated_group_norm_kernel<T><<<dim3((unsigned)n, (unsigned)groups), 256, 0, lm_stream(stream)>>>(
                       y, ldy, gate, ldg, mode, width, groups, static_cast<const T*>(weight), eps, static_cast<T*>(out)));
   return lm_launch_status();
