@@ -384,7 +384,8 @@ AO_B200_API int ao_lm_channel_recurrence(const float* r, int64_t ldr, const floa
  * first_rows (>= keep) positions in first_k / first_v [slots][first_rows][...]; the step's own rows from kn / vn.
  * ao_lm_window_append stores the step's rows, after the last layer that reads the cache has run.
  * tile_first / tile_count: runs of <= tile_rows consecutive rows of one segment (ao_lm_window_attention_plan; 0 = shape not
- * covered). */
+ * covered).  n_split > 1 (<= 64): the keys of a tile are shared out over that many CTAs and a second launch merges their
+ * results (few rows over a long window: a decoded token); workspace of ao_lm_window_attention_workspace_bytes. */
 AO_B200_API int ao_lm_qkv_rotary_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off,
                                       const void* q_bias, const void* k_bias, const void* v_bias, const int32_t* pos,
                                       const float* inv_freq, int rot_dims, int pairing, int64_t n, int q_heads, int k_heads, int d,
@@ -398,7 +399,18 @@ AO_B200_API int ao_lm_window_attention(const float* qn, const void* kn, const vo
                                        const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
                                        const int32_t* tile_count, int n_tiles, int n_maps, int H, int G, int d, int dv,
                                        int window, int keep, float scale, float lambda, int unit_rms, float eps, float out_scale,
-                                       void* out, int64_t ld_out, void* stream);
+                                       int n_split, void* workspace, int64_t workspace_bytes, void* out, int64_t ld_out,
+                                       void* stream);
+AO_B200_API int64_t ao_lm_window_attention_workspace_bytes(int n_tiles, int n_maps, int G, int dv, int n_split);
+/* The same attention for prompt portions on the tensor cores (bf16 storage; d and dv multiples of 16, dv <= 128): tiles of
+ * ao_lm_window_attention_prompt_plan rows (0 = shape not covered), one CTA per (tile, query head). */
+AO_B200_API int ao_lm_window_attention_prompt_plan(int dt, int n_maps, int H, int G, int d, int dv, int* tile_rows);
+AO_B200_API int ao_lm_window_attention_prompt(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
+                                              const void* first_k, const void* first_v, int ring, int first_rows, int dt,
+                                              const int32_t* slot, const int32_t* pos, const int32_t* back,
+                                              const int32_t* tile_first, const int32_t* tile_count, int n_tiles, int n_maps,
+                                              int H, int G, int d, int dv, int window, int keep, float scale, float lambda,
+                                              int unit_rms, float eps, float out_scale, void* out, int64_t ld_out, void* stream);
 
 /* Router over fp32 logits[n][ld] (+ bias, fp32 [E], null: none): the `top` largest logits (ties: lowest index) ->
  * idx[t][top], weight = softmax over the chosen logits only.  extra >= 0: extra_out[t] = sigmoid(logits[t][extra]), a gate

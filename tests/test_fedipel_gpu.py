@@ -319,15 +319,18 @@ def test_retention_rotation_recurrence_and_unit_rms_gate_in_portions(H, d, dv, d
         assert _close(torch.cat(outs), ref, 1e-4), (cuts[:3], tile)
 
 
-def _window_run(q, k, v, cuts, window, keep, scale, lam, ring, first_rows, dtype, slot=1, slots=3, eps=1e-5, out_scale=1.0, unit=1):
+def _window_run(q, k, v, cuts, window, keep, scale, lam, ring, first_rows, dtype, slot=1, slots=3, eps=1e-5, out_scale=1.0, unit=1, n_split=1,
+                tensor=False):
     """window_attention over one sequence cut into portions: prep-less (q, k, v are given rotated), every portion attends
-    over the slot's ring / first-token store and its own rows, then its rows are appended.  -> [T][H][dv] fp32."""
+    over the slot's ring / first-token store and its own rows, then its rows are appended.  -> [T][H][dv] fp32.
+    tensor: the tensor-core form for prompt portions (bf16)."""
     lib, L = _lm()
     T, H, M, d = q.shape
     G, dv = k.shape[1], v.shape[-1]
     tdt, dt = (torch.bfloat16, BF16) if dtype == torch.bfloat16 else (torch.float32, F32)
     tr = __import__("ctypes").c_int()
-    lib.lm_check(L.ao_lm_window_attention_plan(dt, M, H, G, d, dv, __import__("ctypes").byref(tr)), "plan")
+    plan = L.ao_lm_window_attention_prompt_plan if tensor else L.ao_lm_window_attention_plan
+    lib.lm_check(plan(dt, M, H, G, d, dv, __import__("ctypes").byref(tr)), "plan")
     assert tr.value > 0
     rk = torch.full((slots, ring, G * M * d), 50.0, device="cuda", dtype=tdt)       # rubbish that a fresh sequence must not see
     rv = torch.full((slots, ring, G * dv), 50.0, device="cuda", dtype=tdt)
@@ -341,9 +344,13 @@ def _window_run(q, k, v, cuts, window, keep, scale, lam, ring, first_rows, dtype
         qd = q[a:a + c].float().cuda().contiguous()
         kd, vd = k[a:a + c].cuda().to(tdt).contiguous(), v[a:a + c].cuda().to(tdt).contiguous()
         o = torch.zeros(c, H * dv, device="cuda", dtype=tdt)
-        lib.lm_check(L.ao_lm_window_attention(_p(qd), _p(kd), _p(vd), _p(rk), _p(rv), _p(fk), _p(fv), ring, first_rows, dt, _p(sd), _p(pd),
-                                              _p(bd), _p(tf), _p(tc), len(tf), M, H, G, d, dv, window, keep, scale, lam, unit, eps, out_scale,
-                                              _p(o), H * dv, _st()), "window_attention")
+        ws = torch.zeros(max(16, int(L.ao_lm_window_attention_workspace_bytes(len(tf), M, G, dv, n_split))), device="cuda", dtype=torch.uint8)
+        common = (_p(qd), _p(kd), _p(vd), _p(rk), _p(rv), _p(fk), _p(fv), ring, first_rows, dt, _p(sd), _p(pd), _p(bd), _p(tf), _p(tc), len(tf),
+                  M, H, G, d, dv, window, keep, scale, lam, unit, eps, out_scale)
+        if tensor:
+            lib.lm_check(L.ao_lm_window_attention_prompt(*common, _p(o), H * dv, _st()), "window_attention_prompt")
+        else:
+            lib.lm_check(L.ao_lm_window_attention(*common, n_split, _p(ws), ws.numel(), _p(o), H * dv, _st()), "window_attention")
         lib.lm_check(L.ao_lm_window_append(_p(kd), _p(vd), c, G * M * d, G * dv, ring, first_rows, dt, _p(sd), _p(pd), _p(ad), _p(rk), _p(rv),
                                            _p(fk), _p(fv), _st()), "window_append")
         outs.append(o.float())
@@ -362,12 +369,27 @@ def test_window_attention_whole_portions_and_decoding(dtype, H, G, M, d, dv, win
     q = q.float().double()
     ref = O.window_diff_attention(q, k, v, scale, window, keep, lam, 1e-5) * 0.7
     tol = 1e-4 if dtype == torch.float32 else 2e-2
-    for cuts, ring in ([(0, T)], window), (_cuts(T, [1]), window), (_cuts(T, [2, 7, 1, 19]), window + 3), (_cuts(T, [25, 1, 1]), max(window, keep) + 40):
-        got = _window_run(q, k, v, cuts, window, keep, scale, lam, ring, keep + (ring % 3), dtype, out_scale=0.7)
-        assert _close(got, ref, tol), (cuts[:3], ring)
+    for cuts, ring, ns in (([(0, T)], window, 1), (_cuts(T, [1]), window, 1), (_cuts(T, [2, 7, 1, 19]), window + 3, 1),
+                           (_cuts(T, [25, 1, 1]), max(window, keep) + 40, 1), (_cuts(T, [1]), window + 2, 2), (_cuts(T, [9, 1, 3]), window, 5),
+                           ([(0, T)], window, 64)):      # key splits: some shares see no key at all
+        got = _window_run(q, k, v, cuts, window, keep, scale, lam, ring, keep + (ring % 3), dtype, out_scale=0.7, n_split=ns)
+        assert _close(got, ref, tol), (cuts[:3], ring, ns)
 
 
-@pytest.mark.parametrize("how", ["whole", "portions", "decoded"])
+@pytest.mark.parametrize("H,G,M,d,dv,window,keep", [(4, 2, 2, 16, 32, 9, 2), (2, 1, 2, 64, 128, 70, 5), (3, 3, 1, 32, 16, 150, 0), (2, 2, 2, 48, 96, 1, 1),
+                                                    (2, 1, 2, 16, 48, 64, 64)])
+def test_window_attention_tensor_core_form_for_prompt_portions(H, G, M, d, dv, window, keep):
+    T, scale, lam = 200, 0.3, 0.6
+    g = _gen(H * 7 + d)
+    rnd = lambda *s: torch.randn(*s, generator=g).bfloat16().double()
+    q, k, v = rnd(T, H, M, d), rnd(T, G, M, d), rnd(T, G, dv)      # bf16 values: the operands of the tensor-core products are exact
+    ref = O.window_diff_attention(q, k, v, scale, window, keep, lam, 1e-5) * 0.7
+    for cuts, ring in ([(0, T)], window), (_cuts(T, [64, 1, 70, 17]), window + 5), (_cuts(T, [130, 3]), max(window, keep) + 100):
+        got = _window_run(q, k, v, cuts, window, keep, scale, lam, ring, keep + 1, torch.bfloat16, out_scale=0.7, tensor=True)
+        assert _close(got, ref, 1e-2), (cuts[:3], ring)     # what is left is the bf16 rounding of the result
+
+
+@pytest.mark.parametrize("how", ["whole", "portions", "decoded", "tensor"])
 @pytest.mark.parametrize("key,query,seen", [(0, 99, True), (2, 99, True), (3, 99, False), (60, 99, True), (59, 99, False), (99, 99, True),
                                             (100, 99, False), (3, 42, True), (40, 79, True), (39, 79, False), (2, 150, True), (111, 150, True),
                                             (110, 150, False)])
@@ -375,15 +397,23 @@ def test_window_attention_one_dominant_key_inside_and_outside_the_window_and_the
     """Window 40, first 3 tokens kept.  One key matches one query so strongly that, when the mask lets the query see it, map 1
     returns that key's value; map 2 is uniform.  A key one step outside the window, the first token that is not kept, or a
     key in the future must leave no trace."""
-    T, H, G, d, dv, window, keep = 151, 2, 1, 8, 8, 40, 3
+    T, H, G, d, dv, window, keep = 151, 2, 1, 16, 16, 40, 3
     g = _gen(5)
     q, k = torch.zeros(T, H, 2, d, dtype=F64), torch.zeros(T, G, 2, d, dtype=F64)
     v = torch.randn(T, G, dv, generator=g, dtype=F64).float().double()
     mark = torch.zeros(d, dtype=F64)
     mark[3] = 1.0
     q[query, :, 0], k[key, 0, 0] = 30.0 * mark, 30.0 * mark
-    cuts = {"whole": [(0, T)], "portions": _cuts(T, [37, 2, 5]), "decoded": [(0, 38)] + [(i, 1) for i in range(38, T)]}[how]
-    got = _window_run(q, k, v, cuts, window, keep, 1.0, 0.0, 45, 4, torch.float32, unit=0)[query, 0]
+    cuts = {"whole": [(0, T)], "portions": _cuts(T, [37, 2, 5]), "decoded": [(0, 38)] + [(i, 1) for i in range(38, T)],
+            "tensor": _cuts(T, [70, 17])}[how]
+    if how == "tensor":
+        v = v.bfloat16().double()
+        got = _window_run(q, k, v, cuts, window, keep, 1.0, 0.0, 45, 4, torch.bfloat16, unit=0, tensor=True)[query, 0]
+        lo = max(0, query - window + 1)
+        visible = sorted(set(range(min(keep, query + 1))) | set(range(lo, query + 1)))
+        assert _close(got, v[key, 0] if seen else v[visible, 0].mean(0), 1e-2), (key, query)
+        return
+    got = _window_run(q, k, v, cuts, window, keep, 1.0, 0.0, 45, 4, torch.float32, unit=0, n_split=3 if how == "decoded" else 1)[query, 0]
     lo = max(0, query - window + 1)
     visible = sorted(set(range(min(keep, query + 1))) | set(range(lo, query + 1)))
     mean = v[visible, 0].mean(0)
@@ -571,6 +601,26 @@ def test_prefill_equals_token_by_token_and_portions(dtype, name):
         if dtype == torch.float32:
             assert _err(got, whole) < 5e-5      # the same sums, in another order at most
         st.release("p")
+
+
+@pytest.mark.parametrize("min_rows", [1, 1000])
+def test_either_attention_form_for_every_portion_and_batch(monkeypatch, min_rows):
+    """bf16 with head sizes that both attention kernels cover: every step attends with the tensor-core form (min_rows 1, also
+    single decoded tokens) or with the fp32 form (min_rows 1000, also long portions)."""
+    import torchao_fork_b200._models.segment_step as S
+    monkeypatch.setattr(S, "PROMPT_MIN_ROWS", min_rows)
+    cfg = _wide()
+    cfg["layers"][0]["mixer"]["mask"] = {"size": 50, "keep_first": 3}
+    w = O.random_weights(cfg, 29)
+    a, b = _tokens(cfg, 140, 3), _tokens(cfg, 30, 4)
+    ra, rb = O.forward(cfg, w, a), O.forward(cfg, w, b)
+    tol = max(_bf16_tol(cfg, w, a), _bf16_tol(cfg, w, b))
+    m = _model(cfg, w, torch.bfloat16, slots=2)
+    eng, st = m.step_engine, m.states
+    g1 = eng.step([(st.slot_of("a"), a[:100]), (st.slot_of("b"), b[:5])], "all")
+    g2 = eng.step([(st.slot_of("b"), b[5:6]), (st.slot_of("a"), a[100:101])], "all")
+    g3 = eng.step([(st.slot_of("a"), a[101:]), (st.slot_of("b"), b[6:])], "all")
+    assert _within(torch.cat([g1[:100], g2[1:], g3[:39]]), ra, tol) and _within(torch.cat([g1[100:], g2[:1], g3[39:]]), rb, tol)
 
 
 def test_pieces_cut_inside_a_step_both_recurrence_forms_and_both_expert_paths(monkeypatch):

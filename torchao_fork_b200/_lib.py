@@ -201,11 +201,15 @@ LM_SIGNATURES = {
     "ao_lm_window_append": [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "ao_lm_window_attention_plan": [_i32, _i32, _i32, _i32, _i32, _i32, _p32],
     "ao_lm_window_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
-                               _i32, _i32, _i32, _i32, _i32, _f32, _f32, _i32, _f32, _f32, _vp, _i64, _vp],
+                               _i32, _i32, _i32, _i32, _i32, _f32, _f32, _i32, _f32, _f32, _i32, _vp, _i64, _vp, _i64, _vp],
+    "ao_lm_window_attention_workspace_bytes": [_i32, _i32, _i32, _i32, _i32],
+    "ao_lm_window_attention_prompt_plan": [_i32, _i32, _i32, _i32, _i32, _i32, _p32],
+    "ao_lm_window_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                      _i32, _i32, _i32, _i32, _i32, _f32, _f32, _i32, _f32, _f32, _vp, _i64, _vp],
     "ao_lm_router_topk_renorm_logits": [_vp, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp],
     "ao_lm_expert_up_act": [_vp, _vp, _i32, _vp, _i64, _i32, _i64, _i64, _i64, _i32, _vp, _vp],
 }
-_LM_RESTYPES = {"ao_lm_last_cuda_error": ctypes.c_char_p, "ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64, "ao_lm_outer_recurrence_workspace_bytes": _i64, "ao_lm_channel_recurrence_workspace_bytes": _i64,
+_LM_RESTYPES = {"ao_lm_last_cuda_error": ctypes.c_char_p, "ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64, "ao_lm_outer_recurrence_workspace_bytes": _i64, "ao_lm_channel_recurrence_workspace_bytes": _i64, "ao_lm_window_attention_workspace_bytes": _i64,
                 "ao_lm_chunk_attention_workspace_bytes": _i64}
 _lm = None
 _LM_ERRORS = {1: "invalid argument", 2: "unsupported shape", 3: "CUDA launch failed", 4: "workspace too small"}

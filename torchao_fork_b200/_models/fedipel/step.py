@@ -56,9 +56,10 @@ class StepEngine(SegmentStepEngine):
 
     def _attention_plan(self, shape):
         _, maps, H, G, d, dv = shape
-        tr = ctypes.c_int()
+        tr, pr = ctypes.c_int(), ctypes.c_int()
         _lib.lm_check(self.L.ao_lm_window_attention_plan(self.dt, maps, H, G, d, dv, ctypes.byref(tr)), "window_attention_plan")
-        return tr.value, 1 << 30, 0      # tiles may cross any position; one kernel form
+        _lib.lm_check(self.L.ao_lm_window_attention_prompt_plan(self.dt, maps, H, G, d, dv, ctypes.byref(pr)), "window_attention_prompt_plan")
+        return tr.value, 1 << 30, pr.value      # tiles may cross any position
 
     # ------------------------------------------------------------------------------------------------ layers
     def _norm(self, x, y, w, b, st, want_f32=False):
@@ -200,14 +201,20 @@ class StepEngine(SegmentStepEngine):
                                               _p(meta.pos), _p(lay.inv_freq), a.rot.dims, PAIR_INTERLEAVED, n, 2 * H, 2 * G if own else 0,
                                               d, G * dv, dt, _p(qn), _p(kn) if own else None, _p(vn) if own else None, st),
                       "qkv_rotary_prep")
-        tf, tc, nt, _ = meta.attn[("window", 2, H, G, d, dv)]
+        tf, tc, nt, tensor = meta.attn[("window", 2, H, G, d, dv)]
         o = torch.empty(n, H * dv, dtype=tdt, device=dev)
-        _lib.lm_check(L.ao_lm_window_attention(_p(qn), _p(kn), _p(vn), _p(cache.k), _p(cache.v), _p(cache.k_first), _p(cache.v_first),
-                                               cache.ring, cache.first_rows, dt, _p(meta.slot), _p(meta.pos), _p(meta.back), _p(tf),
-                                               _p(tc), nt, 2, H, G, d, dv, min(a.window, cache.ring), min(a.keep, cache.first_rows),
-                                               a.scale, lay.lam, 1, self.cfg.norm_eps, 1.0 - a.diff, _p(o), H * dv, st),
-                      "window_attention")
+        window, keep = min(a.window, cache.ring), min(a.keep, cache.first_rows)
+        common = (_p(qn), _p(kn), _p(vn), _p(cache.k), _p(cache.v), _p(cache.k_first), _p(cache.v_first), cache.ring, cache.first_rows,
+                  dt, _p(meta.slot), _p(meta.pos), _p(meta.back), _p(tf), _p(tc), nt, 2, H, G, d, dv, window, keep, a.scale, lay.lam, 1,
+                  self.cfg.norm_eps, 1.0 - a.diff)
         c = 4
+        if tensor:      # prompt portions: the tensor-core form
+            _lib.lm_check(L.ao_lm_window_attention_prompt(*common, _p(o), H * dv, st), "window_attention_prompt")
+        else:
+            ns = self._splits(nt * G, window + keep)    # few rows over a long window: the keys are shared out over more CTAs
+            ws = torch.empty(max(16, int(L.ao_lm_window_attention_workspace_bytes(nt, 2, G, dv, ns))), dtype=torch.uint8, device=dev)
+            _lib.lm_check(L.ao_lm_window_attention(*common, ns, _p(ws), ws.numel(), _p(o), H * dv, st), "window_attention")
+            c += 1 if ns > 1 else 0
         if self.last_reader[owner] == i:        # nobody reads the old rows any more: the step's rows enter the cache
             _lib.lm_check(L.ao_lm_window_append(_p(kn), _p(vn), n, G * 2 * d, G * dv, cache.ring, cache.first_rows, dt, _p(meta.slot),
                                                 _p(meta.pos), _p(meta.ahead), _p(cache.k), _p(cache.v), _p(cache.k_first),

@@ -11,7 +11,7 @@
 //   gate and normalisation in fp32.
 // 4 warps x 16 rows.  K and V tiles arrive by cp.async in separate groups: the next keys load while the weights meet the
 // values, the next values during the score product.
-#include "lm_common.cuh"
+#include "lm_mma.cuh"
 
 using namespace lm;
 
@@ -21,43 +21,6 @@ constexpr int kPM = 64;      // query rows per CTA
 constexpr int kPN = 64;      // keys per tile
 constexpr int kPWarps = 4;
 constexpr int kPad = 8;      // bf16 elements added to every shared-memory row: 16-byte rows land on distinct banks
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(s));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-// x -> (bf16 part, what is left of x); the remainder is exact in fp32
-__device__ __forceinline__ float split_bf16(float& x) {
-  const float h = __bfloat162float(__float2bfloat16_rn(x));
-  x -= h;
-  return h;
-}
 
 // tanh through one exponential: 1 - 2 / (e^(2x) + 1).  Absolute error of a few 1e-7, which is far below what the bf16
 // operands of this kernel leave in a score; the fp32 kernel keeps tanhf.

@@ -98,7 +98,30 @@ struct WinArgs {
   int unit_rms;
   void* out;                       // [n][ld_out], H * dv per row
   int64_t ld_out;
+  int n_split;                     // > 1: blockIdx.z takes a share of the key blocks and leaves (max, denominator, sums) in ws
+  float* ws;                       // [tiles][G][n_split][kPairs][n_maps][dv + 2]
 };
+
+// a_1 - lambda a_2 (or a_1 alone), optionally divided by its root mean square over the head's dv values, times out_scale:
+// what a warp does with the normalised sums of its (row, query head) pair, lane = value column mod 32.
+template <typename T, int NM>
+__device__ __forceinline__ void finish_pair(const WinArgs& a, const float (&av)[NM][kMaxDvLane], int lane, T* dst) {
+  float val[kMaxDvLane], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < kMaxDvLane; ++e) {
+    float v = av[0][e];
+    if (NM == 2) v -= a.lambda * av[NM - 1][e];
+    val[e] = lane + 32 * e < a.dv ? v : 0.f;
+    ss = fmaf(val[e], val[e], ss);
+  }
+  float k = a.out_scale;
+  if (a.unit_rms) k /= sqrtf(warp_sum(ss) / (float)a.dv + a.eps);
+#pragma unroll
+  for (int e = 0; e < kMaxDvLane; ++e) {
+    const int c = lane + 32 * e;
+    if (c < a.dv) stf(dst + c, val[e] * k);
+  }
+}
 
 // One CTA = a tile of consecutive rows of one segment x one key/value head; a warp owns up to kSlots (row, query head)
 // pairs and keeps the running maximum, denominator and sums of all their maps in registers.  Key index kk of the tile
@@ -144,7 +167,9 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
 #pragma unroll
       for (int e = 0; e < kMaxDvLane; ++e) o[sl][m][e] = 0.f;
     }
-  for (int k0 = 0; k0 < nk; k0 += kKeys) {
+  const int blocks = (nk + kKeys - 1) / kKeys, per = (blocks + a.n_split - 1) / a.n_split;
+  const int k_begin = blockIdx.z * per * kKeys, k_end = min(nk, (int)(blockIdx.z + 1) * per * kKeys);
+  for (int k0 = k_begin; k0 < k_end; k0 += kKeys) {
     __syncthreads();   // the previous block is used up (and, the first time, the queries are in place)
     for (int i = threadIdx.x; i < kKeys * KD; i += blockDim.x) {
       const int jj = i / KD, c = i - jj * KD, kk = k0 + jj;
@@ -230,23 +255,60 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
   for (int sl = 0; sl < kSlots; ++sl) {
     const int pr = warp + sl * kWarps;
     if (pr >= npairs) continue;
+    if (a.n_split > 1) {   // this share's maximum, denominator and sums; the merge kernel finishes the pair
+#pragma unroll
+      for (int m = 0; m < NM; ++m) {
+        float* w = a.ws + (((((int64_t)tile * G + g) * a.n_split + blockIdx.z) * kPairs + pr) * NM + m) * (dv + 2);
+        if (lane == 0) w[0] = mx[sl][m], w[1] = den[sl][m];
+#pragma unroll
+        for (int e = 0; e < kMaxDvLane; ++e)
+          if (lane + 32 * e < dv) w[2 + lane + 32 * e] = o[sl][m][e];
+      }
+      continue;
+    }
     const int r = pr / rep, qh = g * rep + pr % rep;
-    float val[kMaxDvLane], ss = 0.f;
+    float av[NM][kMaxDvLane];
 #pragma unroll
-    for (int e = 0; e < kMaxDvLane; ++e) {
-      float v = o[sl][0][e] / den[sl][0];
-      if (NM == 2) v -= a.lambda * (o[sl][NM - 1][e] / den[sl][NM - 1]);
-      val[e] = lane + 32 * e < dv ? v : 0.f;
-      ss = fmaf(val[e], val[e], ss);
-    }
-    float k = a.out_scale;
-    if (a.unit_rms) k /= sqrtf(warp_sum(ss) / (float)dv + a.eps);
-    T* dst = static_cast<T*>(a.out) + (int64_t)(first + r) * a.ld_out + (int64_t)qh * dv;
+    for (int m = 0; m < NM; ++m)
 #pragma unroll
-    for (int e = 0; e < kMaxDvLane; ++e) {
-      const int c = lane + 32 * e;
-      if (c < dv) stf(dst + c, val[e] * k);
+      for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = o[sl][m][e] / den[sl][m];
+    finish_pair<T, NM>(a, av, lane, static_cast<T*>(a.out) + (int64_t)(first + r) * a.ld_out + (int64_t)qh * dv);
+  }
+}
+
+// The shares of the key splits, merged on a common maximum per (pair, map), then finished like an unsplit pair.
+template <typename T, int NM>
+__global__ void __launch_bounds__(kWarps * 32) window_attention_merge_kernel(WinArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, g = blockIdx.y;
+  const int dv = a.dv, rep = a.H / a.G;
+  const int first = a.tile_first[tile], npairs = a.tile_count[tile] * rep;
+  const int64_t stride = (int64_t)kPairs * NM * (dv + 2);          // from one share to the next
+  for (int pr = warp; pr < npairs; pr += kWarps) {
+    float av[NM][kMaxDvLane];
+#pragma unroll
+    for (int m = 0; m < NM; ++m) {
+      const float* w0 = a.ws + (((((int64_t)tile * a.G + g) * a.n_split) * kPairs + pr) * NM + m) * (dv + 2);
+      float top = -INFINITY;
+      for (int z = lane; z < a.n_split; z += 32) top = fmaxf(top, w0[z * stride]);
+      top = warp_max(top);
+      float den = 0.f;
+#pragma unroll
+      for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = 0.f;
+      for (int z = 0; z < a.n_split; ++z) {
+        const float mz = w0[z * stride];
+        if (mz == -INFINITY) continue;                 // a share that saw no key (uniform over the warp)
+        const float f = expf(mz - top);
+        den = fmaf(w0[z * stride + 1], f, den);
+#pragma unroll
+        for (int e = 0; e < kMaxDvLane; ++e)
+          if (lane + 32 * e < dv) av[m][e] = fmaf(w0[z * stride + 2 + lane + 32 * e], f, av[m][e]);
+      }
+#pragma unroll
+      for (int e = 0; e < kMaxDvLane; ++e) av[m][e] /= den;
     }
+    const int r = pr / rep, qh = g * rep + pr % rep;
+    finish_pair<T, NM>(a, av, lane, static_cast<T*>(a.out) + (int64_t)(first + r) * a.ld_out + (int64_t)qh * dv);
   }
 }
 
@@ -268,7 +330,8 @@ int launch_window(const WinArgs& a, int n_tiles, size_t smem, cudaStream_t st) {
       set = true;
     }
   }
-  kern<<<dim3((unsigned)n_tiles, (unsigned)a.G), kWarps * 32, smem, st>>>(a);
+  kern<<<dim3((unsigned)n_tiles, (unsigned)a.G, (unsigned)a.n_split), kWarps * 32, smem, st>>>(a);
+  if (a.n_split > 1) window_attention_merge_kernel<T, NM><<<dim3((unsigned)n_tiles, (unsigned)a.G), kWarps * 32, 0, st>>>(a);
   return lm_launch_status();
 }
 
@@ -298,6 +361,10 @@ extern "C" int ao_lm_window_append(const void* kn, const void* vn, int64_t n, in
   return lm_launch_status();
 }
 
+extern "C" int64_t ao_lm_window_attention_workspace_bytes(int n_tiles, int n_maps, int G, int dv, int n_split) {
+  return n_split > 1 ? (int64_t)n_tiles * G * n_split * kPairs * n_maps * (dv + 2) * 4 : 0;
+}
+
 extern "C" int ao_lm_window_attention_plan(int dt, int n_maps, int H, int G, int d, int dv, int* tile_rows) {
   LM_CHECK_ARG(tile_rows);
   (void)dt;
@@ -310,16 +377,21 @@ extern "C" int ao_lm_window_attention(const float* qn, const void* kn, const voi
                                       const void* first_k, const void* first_v, int ring, int first_rows, int dt,
                                       const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
                                       const int32_t* tile_count, int n_tiles, int n_maps, int H, int G, int d, int dv, int window,
-                                      int keep, float scale, float lambda, int unit_rms, float eps, float out_scale, void* out,
-                                      int64_t ld_out, void* stream) {
+                                      int keep, float scale, float lambda, int unit_rms, float eps, float out_scale, int n_split,
+                                      void* workspace, int64_t workspace_bytes, void* out, int64_t ld_out, void* stream) {
   LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && slot && pos && back && tile_first && tile_count && out);
   LM_CHECK_ARG(n_tiles > 0 && window > 0 && keep >= 0 && ring >= window && first_rows >= keep && (first_rows == 0 || (first_k && first_v)));
-  LM_CHECK_ARG(G > 0 && G <= 65535 && (n_maps == 1 || n_maps == 2));
+  LM_CHECK_ARG(G > 0 && G <= 65535 && (n_maps == 1 || n_maps == 2) && n_split >= 1 && n_split <= 64);
+  if (n_split > 1) {
+    LM_CHECK_ARG(workspace);
+    if (workspace_bytes < ao_lm_window_attention_workspace_bytes(n_tiles, n_maps, G, dv, n_split)) return AO_B200_ERR_WORKSPACE;
+  }
   if (win_tile_rows(H, G) == 0 || dv > 32 * kMaxDvLane) return AO_B200_ERR_UNSUPPORTED;
   const size_t smem = win_smem(n_maps, d, dv);
   if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
   WinArgs a{qn, kn, vn, ring_k, ring_v, first_k ? first_k : ring_k, first_v ? first_v : ring_v, ring, first_rows, slot, pos, back,
-            tile_first, tile_count, H, G, d, dv, window, keep, scale, lambda, out_scale, eps, unit_rms, out, ld_out};
+            tile_first, tile_count, H, G, d, dv, window, keep, scale, lambda, out_scale, eps, unit_rms, out, ld_out, n_split,
+            static_cast<float*>(workspace)};
   const cudaStream_t st = lm_stream(stream);
   LM_DISPATCH(dt, {
     if (n_maps == 2) return launch_window<T, 2>(a, n_tiles, smem, st);
