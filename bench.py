@@ -592,9 +592,10 @@ def main():
     ap.add_argument("--steps", type=int, default=200)  # reference: 200 new tokens per sample (generate.py:264)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-int4", choices=sorted(WORKLOADS) + ["bitipel-layers", "tadolix-layers", "rutusun-layers"],
-                    help="bitipel-layers / tadolix-layers / rutusun-layers: prefill / decode of that family's layers at real sizes beside the Llama "
-                         "family at equal size (benchmarks/bitipel_bench.py, tadolix_bench.py, rutusun_bench.py; their own JSON line, not "
+    ap.add_argument("--workload", default="llama3-8b-int4", choices=sorted(WORKLOADS) + ["bitipel-layers", "tadolix-layers", "rutusun-layers", "fedipel-layers"],
+                    help="bitipel-layers / tadolix-layers / rutusun-layers / fedipel-layers: prefill / decode of that family's layers at real sizes "
+                         "beside the closest other family at equal size (benchmarks/bitipel_bench.py, tadolix_bench.py, rutusun_bench.py, "
+                         "fedipel_bench.py; their own JSON line, not "
                          "the headline metric)")
     ap.add_argument("--batch-size", type=int, default=1)
     ap.add_argument("--temperature", type=float, default=0.8)
@@ -612,6 +613,11 @@ def main():
         assert args.impl == "b200" and args.gpus == 1, "tadolix-layers is a one-GPU measurement of this repo's kernels"
         from benchmarks import tadolix_bench
         emit(tadolix_bench.run())
+        return
+    if args.workload == "fedipel-layers":
+        assert args.impl == "b200" and args.gpus == 1, "fedipel-layers is a one-GPU measurement of this repo's kernels"
+        from benchmarks import fedipel_bench
+        emit(fedipel_bench.run())
         return
     if args.workload == "rutusun-layers":
         assert args.impl == "b200" and args.gpus == 1, "rutusun-layers is a one-GPU measurement of this repo's kernels"

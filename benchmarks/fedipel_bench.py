@@ -149,3 +149,105 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     res["rutusun_sink_attention_decode"] = {"keys": decode_ctx, "splits": ns2, "us": round(ms * 1e3, 2), "cache_bytes": byts, **frac(byts, ms)}
     return res, dict(L=L, _lib=_lib, cfg=cfg, ret=ret, wkv=wkv, att=att, W=W, n=n, flush=flush, bf=bf, f32=f32, i32=i32, p=p, st=st,
                      slot=slot, pos=pos, back=back, last=last, cnt=cnt, frac=frac, hbm=hbm, REC_TILE=REC_TILE, scan_tiles=scan_tiles)
+
+
+def recurrence_and_row_numbers(res, k):
+    """Second half of the kernels alone: the two matrix-state recurrences and the row kernels."""
+    L, _lib, cfg, ret, wkv, W, n = k["L"], k["_lib"], k["cfg"], k["ret"], k["wkv"], k["W"], k["n"]
+    flush, bf, f32, i32, p, st, frac = k["flush"], k["bf"], k["f32"], k["i32"], k["p"], k["st"], k["frac"]
+    slot, pos, back, last, cnt = k["slot"], k["pos"], k["back"], k["last"], k["cnt"]
+    seg_f, seg_c = i32([0]), i32([n])
+    rtf, rtc, rs0, rsn = [i32(t) for t in k["scan_tiles"](np.array([0]), np.array([n]), k["REC_TILE"])]
+
+    # ---- time mixing (decay per token and key channel, bonus) beside the fixed-decay recurrence that retention shares with
+    # the Rutusun family's lightning mixer, at the same heads and head sizes
+    Hh, dd = wkv.heads, wkv.dim
+    r_, k_, v_, z_ = (torch.randn(n, Hh * dd, **f32) for _ in range(4))
+    w0, u = torch.randn(Hh * dd, **bf) - 1.5, torch.randn(Hh, dd, **bf)
+    state, o = torch.zeros(1, Hh, dd, dd, **f32), torch.empty(n, Hh * dd, **f32)
+    hsrc, shift = torch.randn(n, W, **f32), torch.zeros(1, W, **f32)
+    cws = torch.empty(int(L.ao_lm_channel_recurrence_workspace_bytes(len(rtf), n, Hh, dd, dd)) // 4, **f32)
+    ows = torch.empty(int(L.ao_lm_outer_recurrence_workspace_bytes(len(rtf), n, Hh, dd, dd)) // 4, **f32)
+    a_head = torch.full((Hh,), 0.97, **f32)
+
+    def chan(rows, sf_, sc, ps, tiled):
+        _lib.lm_check(L.ao_lm_channel_recurrence(p(r_), Hh * dd, p(k_), Hh * dd, p(v_), Hh * dd, p(z_), Hh * dd, p(w0), p(u), 0, Hh, dd, dd,
+                                                 p(state), p(slot), p(ps), p(sf_), p(sc), len(rtf) if tiled else 1, p(rs0) if tiled else None,
+                                                 p(rsn) if tiled else None, 1 if tiled else 0, rows, p(cws) if tiled else None, p(hsrc),
+                                                 p(shift), W, p(o), Hh * dd, st), "channel_recurrence")
+
+    def outer(rows, sf_, sc, ps, tiled):
+        _lib.lm_check(L.ao_lm_outer_recurrence(p(r_), Hh * dd, p(k_), Hh * dd, p(v_), Hh * dd, 0, None, None, Hh, p(a_head), None, Hh, Hh, dd,
+                                               dd, p(state), p(slot), p(ps), p(sf_), p(sc), len(rtf) if tiled else 1, p(rs0) if tiled else None,
+                                               p(rsn) if tiled else None, 1 if tiled else 0, rows, p(ows) if tiled else None, p(o), Hh * dd,
+                                               st), "outer_recurrence")
+    flops = 4.0 * n * Hh * dd * dd
+    for key, fn, streams in (("time_mixing_recurrence", chan, 5), ("fixed_decay_recurrence_same_shape", outer, 4)):
+        ms = timed(lambda: fn(n, rtf, rtc, pos, True), flush=flush)
+        byts = n * Hh * dd * 4 * streams
+        res[key + "_prefill"] = {"tokens": n, "heads": Hh, "d": dd, "dv": dd, "ms": round(ms, 4), "fp32_tflops": round(flops / ms / 1e9, 2),
+                                 "frac_fp32_fma_nominal": round(flops / ms / 1e9 / FP32_TFLOPS, 4), **frac(byts, ms)}
+        ms = timed(lambda: fn(1, seg_f, cnt, last, False), flush=flush)
+        byts = 2 * Hh * dd * dd * 4      # the state is read and written once
+        res[key + "_decode"] = {"us": round(ms * 1e3, 2), "state_bytes": byts // 2, **frac(byts, ms)}
+
+    # ---- row kernels over a prompt: residual add + layer norm beside the Rutusun family's post-norm residual (the same
+    # traffic: x read and written, y read, h written); token shift; rotations; the gated unit-RMS norm in both gate modes
+    x, y, h = torch.randn(n, W, **f32), torch.randn(n, W, **f32), torch.empty(n, W, **bf)
+    wa, wb_ = torch.ones(W, **bf), torch.zeros(W, **bf)
+
+    def add_ln():
+        _lib.lm_check(L.ao_lm_add_layer_norm(p(x), p(y), 0.01, None, n, W, p(wa), p(wb_), 0, 1e-6, None, p(h), st), "add_layer_norm")
+
+    def post():
+        _lib.lm_check(L.ao_lm_postnorm_residual(p(x), p(y), 1, None, p(wa), None, None, p(wa), 0, 1e-6, n, W, p(h), st), "postnorm_residual")
+    byts = n * W * (4 + 4 + 4 + 2)
+    res["add_layer_norm_prefill"] = {"ms": round(ms := timed(add_ln, flush=flush), 4), **frac(byts, ms)}
+    res["rutusun_postnorm_residual_prefill"] = {"ms": round(ms := timed(post, flush=flush), 4), **frac(byts, ms)}
+    mu, mixes = torch.rand(5, W, **bf), torch.empty(5, n, W, **bf)
+
+    def shift_mix():
+        _lib.lm_check(L.ao_lm_token_shift_mix(p(x), p(mu), 5, 0, p(shift), p(slot), p(pos), p(back), n, W, p(mixes), st), "token_shift_mix")
+    res["token_shift_mix_prefill"] = {"ms": round(ms := timed(shift_mix, flush=flush), 4), **frac(n * W * (4 + 5 * 2), ms)}
+    Hr, dr, dvr = ret.heads, ret.dim, ret.vdim
+    ld = 2 * Hr * (dr + dvr)
+    proj = torch.randn(n, ld, **f32)
+    inv = ret.rot.inv_freq(proj.device)
+
+    def rotary():
+        _lib.lm_check(L.ao_lm_rotary_rows(p(proj), ld, n, p(pos), p(inv), ret.rot.dims, 1, dr, 0, Hr, 1.0, Hr * dr, Hr, 0.999, st), "rotary_rows")
+    res["rotary_rows_prefill"] = {"ms": round(ms := timed(rotary, flush=flush), 4), **frac(n * 2 * Hr * dr * 8, ms)}
+    a = k["att"]
+    H, G, d, dv = a.heads, a.kv_heads, a.dim, a.vdim
+    lda = 2 * H * d + 2 * G * d + G * dv
+    pj = torch.randn(n, lda, **f32)
+    qb, kb, vb = torch.zeros(2 * H * d, **bf), torch.zeros(2 * G * d, **bf), torch.zeros(G * dv, **bf)
+    qn, kn, vn = torch.empty(n, 2 * H, d, **f32), torch.empty(n, 2 * G, d, **bf), torch.empty(n, G * dv, **bf)
+    inv_a = a.rot.inv_freq(proj.device)
+
+    def prep():
+        _lib.lm_check(L.ao_lm_qkv_rotary_prep(p(pj), lda, 0, 2 * H * d, 2 * H * d + 2 * G * d, p(qb), p(kb), p(vb), p(pos), p(inv_a),
+                                              a.rot.dims, 0, n, 2 * H, 2 * G, d, G * dv, 0, p(qn), p(kn), p(vn), st), "qkv_rotary_prep")
+    res["qkv_rotary_prep_prefill"] = {"ms": round(ms := timed(prep, flush=flush), 4),
+                                      **frac(n * (lda * 4 + 2 * H * d * 4 + (2 * G * d + G * dv) * 2), ms)}
+    rec, gate, go = torch.randn(n, Hr * dvr, **f32), torch.randn(n, Hr * dvr, **f32), torch.empty(n, Hr * dvr, **bf)
+    nw = torch.ones(Hr * dvr, **bf)
+    for key, mode, wt in (("unit_rms_silu_gate_prefill", 2, None), ("rutusun_gated_norm_sigmoid_prefill", 0, nw)):
+        def gnorm():
+            _lib.lm_check(L.ao_lm_gated_group_norm(p(rec), Hr * dvr, p(gate), Hr * dvr, mode, n, Hr * dvr, Hr if mode == 2 else 1, p(wt), 0,
+                                                   1e-6, p(go), st), "gated_group_norm")
+        res[key] = {"ms": round(ms := timed(gnorm, flush=flush), 4), **frac(n * Hr * dvr * (4 + 4 + 2), ms)}
+    return res
+
+
+def run(sizes=(("Fedipel-2k", "Rutusun-2k"), ("Fedipel-4k", "Rutusun-4k")), prompt_len=2048, decode_ctx=1536, decode_steps=64):
+    out = {"metric": "fedipel_layers_prefill_decode", "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "sizes": {}}
+    for name, other in sizes:
+        res, k = kernel_numbers(name, prompt_len, decode_ctx)
+        out["sizes"][name] = {"models": model_numbers(name, other, prompt_len, decode_ctx, decode_steps),
+                              "kernels": recurrence_and_row_numbers(res, k)}
+    return out
+
+
+if __name__ == "__main__":
+    print(json.dumps(run()))

@@ -68,16 +68,9 @@ __global__ void __launch_bounds__(kWarps * 32) channel_recurrence_kernel(ChanArg
     S[i] = (!fresh && c < dv && ch < d) ? srow[(int64_t)ch * dv + c] : 0.f;
     ub[i] = (MODE != 2 && A.bonus && ch < d) ? ldf(static_cast<const T*>(A.bonus) + (int64_t)h * d + ch) : 0.f;
   }
-  if (MODE == 1 && blockIdx.z == 0) {        // the decays' running products, once per (tile, head): a thread per channel
-    for (int ch = threadIdx.x; ch < d; ch += blockDim.x) {
-      float pr = 1.f;
-      for (int j = 0; j < count; ++j) {
-        A.pcum[((int64_t)(first + j) * A.H + h) * d + ch] = pr;
-        pr *= decay_of<T>(A, first + j, h, ch);
-      }
-      A.ptot[((int64_t)seg * A.H + h) * d + ch] = pr;
-    }
-  }
+  // MODE 1: the decays' running products, once per (tile, head): thread ch follows its channel through the staged rows
+  const bool products = MODE == 1 && blockIdx.z == 0 && (int)threadIdx.x < d;
+  float run = 1.f;
   if (MODE == 0 && A.shift_state && h == 0 && blockIdx.z == 0) {
     const float* src = A.shift_src + (int64_t)(first + count - 1) * A.shift_width;
     float* dst = A.shift_state + (int64_t)A.slot[first] * A.shift_width;
@@ -104,25 +97,40 @@ __global__ void __launch_bounds__(kWarps * 32) channel_recurrence_kernel(ChanArg
         vs[j][e] = cc < dv ? A.v[(int64_t)(first + t0 + j) * A.ldv + (int64_t)h * dv + cc] : 0.f;
       }
     __syncthreads();
+    if (products) {
+      for (int j = 0; j < nb; ++j) {
+        A.pcum[((int64_t)(first + t0 + j) * A.H + h) * d + threadIdx.x] = run;
+        run *= wsh[j][threadIdx.x];
+      }
+    }
     for (int j = 0; j < nb; ++j) {
       float o0 = 0.f, o1 = 0.f;
       if (MODE != 2) {
         const float vv = vs[j][lane];
 #pragma unroll
-        for (int i = 0; i < DR; i += 2) {
+        for (int i = 0; i < DR; i += 4) {      // four channels per 16-byte read of the staged rows
           const int ch = warp * DR + i;
-          const float kv0 = ks[j][ch] * vv, kv1 = ks[j][ch + 1] * vv;
-          o0 = fmaf(rs[j][ch], fmaf(ub[i], kv0, S[i]), o0);
-          o1 = fmaf(rs[j][ch + 1], fmaf(ub[i + 1], kv1, S[i + 1]), o1);
-          S[i] = fmaf(wsh[j][ch], S[i], kv0);
-          S[i + 1] = fmaf(wsh[j][ch + 1], S[i + 1], kv1);
+          const float4 r4 = *reinterpret_cast<const float4*>(&rs[j][ch]), k4 = *reinterpret_cast<const float4*>(&ks[j][ch]);
+          const float4 w4 = *reinterpret_cast<const float4*>(&wsh[j][ch]);
+          const float kv0 = k4.x * vv, kv1 = k4.y * vv, kv2 = k4.z * vv, kv3 = k4.w * vv;
+          o0 = fmaf(r4.x, fmaf(ub[i], kv0, S[i]), o0);
+          o1 = fmaf(r4.y, fmaf(ub[i + 1], kv1, S[i + 1]), o1);
+          o0 = fmaf(r4.z, fmaf(ub[i + 2], kv2, S[i + 2]), o0);
+          o1 = fmaf(r4.w, fmaf(ub[i + 3], kv3, S[i + 3]), o1);
+          S[i] = fmaf(w4.x, S[i], kv0);
+          S[i + 1] = fmaf(w4.y, S[i + 1], kv1);
+          S[i + 2] = fmaf(w4.z, S[i + 2], kv2);
+          S[i + 3] = fmaf(w4.w, S[i + 3], kv3);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < DR; i += 2) {
+        for (int i = 0; i < DR; i += 4) {
           const int ch = warp * DR + i;
-          o0 = fmaf(rs[j][ch] * wsh[j][ch], S[i], o0);
-          o1 = fmaf(rs[j][ch + 1] * wsh[j][ch + 1], S[i + 1], o1);
+          const float4 r4 = *reinterpret_cast<const float4*>(&rs[j][ch]), w4 = *reinterpret_cast<const float4*>(&wsh[j][ch]);
+          o0 = fmaf(r4.x * w4.x, S[i], o0);
+          o1 = fmaf(r4.y * w4.y, S[i + 1], o1);
+          o0 = fmaf(r4.z * w4.z, S[i + 2], o0);
+          o1 = fmaf(r4.w * w4.w, S[i + 3], o1);
         }
       }
       op[warp][j][lane] = o0 + o1;
@@ -138,6 +146,7 @@ __global__ void __launch_bounds__(kWarps * 32) channel_recurrence_kernel(ChanArg
       *dst = MODE == 2 ? *dst + o : o;
     }
   }
+  if (products) A.ptot[((int64_t)seg * A.H + h) * d + threadIdx.x] = run;
   if (MODE != 2) {
 #pragma unroll
     for (int i = 0; i < DR; ++i) {

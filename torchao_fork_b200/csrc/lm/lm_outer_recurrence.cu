@@ -431,6 +431,45 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int64_t ldy
   }
 }
 
+// The same for small groups (a head's values): a warp per group, the group's values in registers between the sum of squares
+// and the output.  grid (rows, ceil(groups / 8)), 8 warps.
+constexpr int kGroupPerLane = 16;     // groups of up to 32 * 16 values
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float* __restrict__ y, int64_t ldy,
+                                                                   const float* __restrict__ gate, int64_t ldg, int mode,
+                                                                   int64_t width, int groups, const T* __restrict__ weight, float eps,
+                                                                   T* __restrict__ out) {
+  const int lane = threadIdx.x & 31, grp = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (grp >= groups) return;
+  const int64_t t = blockIdx.x;
+  const int per = (int)(width / groups);
+  const int64_t c0 = (int64_t)grp * per;
+  const float* yr = y + t * ldy + c0;
+  const float* gr = gate + t * ldg + c0;
+  float v[kGroupPerLane], z[kGroupPerLane], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < kGroupPerLane; ++e) {
+    const int c = lane + 32 * e;
+    v[e] = c < per ? yr[c] : 0.f;
+    z[e] = c < per ? gr[c] : 0.f;
+    if (mode == 1) v[e] *= z[e] / (1.f + expf(-z[e]));
+    ss = fmaf(v[e], v[e], ss);
+  }
+  const float k = 1.f / sqrtf(warp_sum(ss) / (float)per + eps);
+#pragma unroll
+  for (int e = 0; e < kGroupPerLane; ++e) {
+    const int c = lane + 32 * e;
+    if (c >= per) continue;
+    const float wt = weight ? ldf(weight + c0 + c) : 1.f;
+    float r = v[e] * k * wt;
+    if (mode == 2)
+      r *= z[e] / (1.f + expf(-z[e]));
+    else if (mode == 0)
+      r /= 1.f + expf(-z[e]);
+    stf(out + t * width + c0 + c, r);
+  }
+}
+
 }  // namespace
 
 extern "C" int64_t ao_lm_outer_recurrence_workspace_bytes(int n_tiles, int64_t n, int H, int d, int dv) {
@@ -488,6 +527,11 @@ extern "C" int ao_lm_gated_group_norm(const float* y, int64_t ldy, const float* 
                                       int64_t width, int groups, const void* weight, int dt, float eps, void* out, void* stream) {
   LM_CHECK_ARG(y && gate && out && n > 0 && width > 0 && groups > 0 && groups <= 65535 && width % groups == 0);
   LM_CHECK_ARG(mode == 0 || mode == 1 || mode == 2);
+  if (groups > 1 && width / groups <= 32 * kGroupPerLane) {
+    LM_DISPATCH(dt, gated_group_norm_warp_kernel<T><<<dim3((unsigned)n, (unsigned)((groups + 7) / 8)), 256, 0, lm_stream(stream)>>>(
+                        y, ldy, gate, ldg, mode, width, groups, static_cast<const T*>(weight), eps, static_cast<T*>(out)));
+    return lm_launch_status();
+  }
   LM_DISPATCH(dt, gated_group_norm_kernel<T><<<dim3((unsigned)n, (unsigned)groups), 256, 0, lm_stream(stream)>>>(
                       y, ldy, gate, ldg, mode, width, groups, static_cast<const T*>(weight), eps, static_cast<T*>(out)));
   return lm_launch_status();

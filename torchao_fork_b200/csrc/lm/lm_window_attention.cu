@@ -289,20 +289,29 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_merge_kernel(Win
 #pragma unroll
     for (int m = 0; m < NM; ++m) {
       const float* w0 = a.ws + (((((int64_t)tile * a.G + g) * a.n_split) * kPairs + pr) * NM + m) * (dv + 2);
-      float top = -INFINITY;
-      for (int z = lane; z < a.n_split; z += 32) top = fmaxf(top, w0[z * stride]);
-      top = warp_max(top);
-      float den = 0.f;
+      // lane z (and z + 32: at most 64 shares) holds share z's maximum and denominator; a share that saw no key weighs 0
+      const int za = lane, zb = lane + 32;
+      const float ma = za < a.n_split ? w0[za * stride] : -INFINITY, mb = zb < a.n_split ? w0[zb * stride] : -INFINITY;
+      const float da = za < a.n_split ? w0[za * stride + 1] : 0.f, db = zb < a.n_split ? w0[zb * stride + 1] : 0.f;
+      const float top = warp_max(fmaxf(ma, mb));
+      const float fa = ma == -INFINITY ? 0.f : expf(ma - top), fb = mb == -INFINITY ? 0.f : expf(mb - top);
+      const float den = warp_sum(fmaf(da, fa, db * fb));
 #pragma unroll
       for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = 0.f;
-      for (int z = 0; z < a.n_split; ++z) {
-        const float mz = w0[z * stride];
-        if (mz == -INFINITY) continue;                 // a share that saw no key (uniform over the warp)
-        const float f = expf(mz - top);
-        den = fmaf(w0[z * stride + 1], f, den);
+      for (int z0 = 0; z0 < a.n_split; z0 += 8) {      // eight shares' sums in flight
+        float v[8][kMaxDvLane];
 #pragma unroll
-        for (int e = 0; e < kMaxDvLane; ++e)
-          if (lane + 32 * e < dv) av[m][e] = fmaf(w0[z * stride + 2 + lane + 32 * e], f, av[m][e]);
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int e = 0; e < kMaxDvLane; ++e)
+            v[j][e] = (z0 + j < a.n_split && lane + 32 * e < dv) ? w0[(z0 + j) * stride + 2 + lane + 32 * e] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int z = z0 + j;
+          const float f = __shfl_sync(0xffffffffu, z < 32 ? fa : fb, z & 31);
+#pragma unroll
+          for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = fmaf(v[j][e], f, av[m][e]);
+        }
       }
 #pragma unroll
       for (int e = 0; e < kMaxDvLane; ++e) av[m][e] /= den;
