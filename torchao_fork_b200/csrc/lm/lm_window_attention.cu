@@ -34,7 +34,8 @@ __global__ void qkv_rotary_prep_kernel(const float* __restrict__ proj, int64_t l
   const float p = (float)pos[t];
   const float* row = proj + t * ld;
   const int half = rot_dims / 2, per = d - half;
-  for (int i = threadIdx.x; i < (q_heads + k_heads) * per; i += blockDim.x) {
+  const int tid = blockIdx.y * blockDim.x + threadIdx.x, nth = gridDim.y * blockDim.x;   // a row may be shared by several CTAs
+  for (int i = tid; i < (q_heads + k_heads) * per; i += nth) {
     const int hd = i / per, e = i - hd * per;
     const bool is_q = hd < q_heads;
     const int64_t ho = (int64_t)(is_q ? hd : hd - q_heads) * d;
@@ -63,7 +64,7 @@ __global__ void qkv_rotary_prep_kernel(const float* __restrict__ proj, int64_t l
     }
   }
   if (k_heads > 0)
-    for (int c = threadIdx.x; c < v_width; c += blockDim.x)
+    for (int c = tid; c < v_width; c += nth)
       stf(vn + t * v_width + c, row[v_off + c] + (v_bias ? ldf(v_bias + c) : 0.f));
 }
 
@@ -277,45 +278,75 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
 }
 
 // The shares of the key splits, merged on a common maximum per (pair, map), then finished like an unsplit pair.
+// One CTA per (tile, key/value head, pair): warp w merges shares w, w + 8, ... (all their loads in flight at once) and
+// leaves its (maximum, denominator, sums) in shared memory; a thread per value column merges the eight; warp 0 finishes.
 template <typename T, int NM>
 __global__ void __launch_bounds__(kWarps * 32) window_attention_merge_kernel(WinArgs a) {
+  extern __shared__ float sm[];    // [kWarps][NM][dv + 2], then [NM][dv]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, g = blockIdx.y;
+  const int tile = blockIdx.x, g = blockIdx.y, pr = blockIdx.z;
   const int dv = a.dv, rep = a.H / a.G;
   const int first = a.tile_first[tile], npairs = a.tile_count[tile] * rep;
+  if (pr >= npairs) return;
   const int64_t stride = (int64_t)kPairs * NM * (dv + 2);          // from one share to the next
-  for (int pr = warp; pr < npairs; pr += kWarps) {
+  constexpr int kPer = 64 / kWarps;                                // shares per warp at most
+  float* part = sm;
+  float* fin = sm + (size_t)kWarps * NM * (dv + 2);
+#pragma unroll
+  for (int m = 0; m < NM; ++m) {
+    const float* w0 = a.ws + (((((int64_t)tile * a.G + g) * a.n_split) * kPairs + pr) * NM + m) * (dv + 2);
+    float mz[kPer], dz[kPer], v[kPer][kMaxDvLane];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int z = warp + j * kWarps;
+      const bool in = z < a.n_split;
+      mz[j] = in ? w0[z * stride] : -INFINITY;
+      dz[j] = in ? w0[z * stride + 1] : 0.f;
+#pragma unroll
+      for (int e = 0; e < kMaxDvLane; ++e) v[j][e] = (in && lane + 32 * e < dv) ? w0[z * stride + 2 + lane + 32 * e] : 0.f;
+    }
+    float top = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) top = fmaxf(top, mz[j]);
+    float den = 0.f, acc[kMaxDvLane];
+#pragma unroll
+    for (int e = 0; e < kMaxDvLane; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const float f = mz[j] == -INFINITY ? 0.f : expf(mz[j] - top);     // a share that saw no key weighs nothing
+      den = fmaf(dz[j], f, den);
+#pragma unroll
+      for (int e = 0; e < kMaxDvLane; ++e) acc[e] = fmaf(v[j][e], f, acc[e]);
+    }
+    float* mine = part + ((size_t)warp * NM + m) * (dv + 2);
+    if (lane == 0) mine[0] = top, mine[1] = den;
+#pragma unroll
+    for (int e = 0; e < kMaxDvLane; ++e)
+      if (lane + 32 * e < dv) mine[2 + lane + 32 * e] = acc[e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < NM * dv; i += blockDim.x) {
+    const int m = i / dv, c = i - m * dv;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) top = fmaxf(top, part[((size_t)w * NM + m) * (dv + 2)]);
+    float den = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* pw = part + ((size_t)w * NM + m) * (dv + 2);
+      const float f = pw[0] == -INFINITY ? 0.f : expf(pw[0] - top);
+      den = fmaf(pw[1], f, den);
+      acc = fmaf(pw[2 + c], f, acc);
+    }
+    fin[i] = acc / den;
+  }
+  __syncthreads();
+  if (warp == 0) {
     float av[NM][kMaxDvLane];
 #pragma unroll
-    for (int m = 0; m < NM; ++m) {
-      const float* w0 = a.ws + (((((int64_t)tile * a.G + g) * a.n_split) * kPairs + pr) * NM + m) * (dv + 2);
-      // lane z (and z + 32: at most 64 shares) holds share z's maximum and denominator; a share that saw no key weighs 0
-      const int za = lane, zb = lane + 32;
-      const float ma = za < a.n_split ? w0[za * stride] : -INFINITY, mb = zb < a.n_split ? w0[zb * stride] : -INFINITY;
-      const float da = za < a.n_split ? w0[za * stride + 1] : 0.f, db = zb < a.n_split ? w0[zb * stride + 1] : 0.f;
-      const float top = warp_max(fmaxf(ma, mb));
-      const float fa = ma == -INFINITY ? 0.f : expf(ma - top), fb = mb == -INFINITY ? 0.f : expf(mb - top);
-      const float den = warp_sum(fmaf(da, fa, db * fb));
+    for (int m = 0; m < NM; ++m)
 #pragma unroll
-      for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = 0.f;
-      for (int z0 = 0; z0 < a.n_split; z0 += 8) {      // eight shares' sums in flight
-        float v[8][kMaxDvLane];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-          for (int e = 0; e < kMaxDvLane; ++e)
-            v[j][e] = (z0 + j < a.n_split && lane + 32 * e < dv) ? w0[(z0 + j) * stride + 2 + lane + 32 * e] : 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int z = z0 + j;
-          const float f = __shfl_sync(0xffffffffu, z < 32 ? fa : fb, z & 31);
-#pragma unroll
-          for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = fmaf(v[j][e], f, av[m][e]);
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < kMaxDvLane; ++e) av[m][e] /= den;
-    }
+      for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = lane + 32 * e < dv ? fin[m * dv + lane + 32 * e] : 0.f;
     const int r = pr / rep, qh = g * rep + pr % rep;
     finish_pair<T, NM>(a, av, lane, static_cast<T*>(a.out) + (int64_t)(first + r) * a.ld_out + (int64_t)qh * dv);
   }
@@ -340,7 +371,10 @@ int launch_window(const WinArgs& a, int n_tiles, size_t smem, cudaStream_t st) {
     }
   }
   kern<<<dim3((unsigned)n_tiles, (unsigned)a.G, (unsigned)a.n_split), kWarps * 32, smem, st>>>(a);
-  if (a.n_split > 1) window_attention_merge_kernel<T, NM><<<dim3((unsigned)n_tiles, (unsigned)a.G), kWarps * 32, 0, st>>>(a);
+  if (a.n_split > 1) {
+    const size_t msm = ((size_t)kWarps * NM * (a.dv + 2) + (size_t)NM * a.dv) * sizeof(float);      // <= 19 KB
+    window_attention_merge_kernel<T, NM><<<dim3((unsigned)n_tiles, (unsigned)a.G, kPairs), kWarps * 32, msm, st>>>(a);
+  }
   return lm_launch_status();
 }
 
@@ -352,7 +386,11 @@ extern "C" int ao_lm_qkv_rotary_prep(const float* proj, int64_t ld, int64_t q_of
                                      float* qn, void* kn, void* vn, void* stream) {
   LM_CHECK_ARG(proj && pos && qn && n > 0 && q_heads > 0 && k_heads >= 0 && d > 0 && (k_heads == 0 || (kn && vn && v_width > 0)));
   LM_CHECK_ARG(rot_dims >= 0 && rot_dims <= d && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq) && (pairing == 0 || pairing == 1));
-  LM_DISPATCH(dt, qkv_rotary_prep_kernel<T><<<(unsigned)n, 256, 0, lm_stream(stream)>>>(
+  // few rows (decoded tokens): several CTAs per row, so that no thread walks more than a few coordinates
+  const int64_t items = (int64_t)(q_heads + k_heads) * (d - rot_dims / 2);
+  const int64_t room = (592 + n - 1) / n, want = (items + 511) / 512;
+  const unsigned parts = n < 296 ? (unsigned)(want > room ? room : want < 1 ? 1 : want) : 1u;
+  LM_DISPATCH(dt, qkv_rotary_prep_kernel<T><<<dim3((unsigned)n, parts), 256, 0, lm_stream(stream)>>>(
                       proj, ld, q_off, k_off, v_off, static_cast<const T*>(q_bias), static_cast<const T*>(k_bias),
                       static_cast<const T*>(v_bias), pos, inv_freq, rot_dims, pairing, q_heads, k_heads, d, v_width, qn,
                       static_cast<T*>(kn), static_cast<T*>(vn)));
