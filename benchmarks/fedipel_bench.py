@@ -129,7 +129,7 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     one, last, zero, cnt = i32([0]), i32([decode_ctx]), i32([0]), i32([1])
     o1 = torch.empty(1, H * dv, **bf)
     ns = max(1, min(-(-(C + 4) // 32), -(-4 * 148 // G), 64))      # what the step function picks for one sequence
-    aws = torch.empty(max(16, int(L.ao_lm_window_attention_workspace_bytes(1, 2, G, dv, ns))), dtype=torch.uint8, device=dev)
+    aws = torch.empty(max(16, int(L.ao_lm_window_attention_workspace_bytes(1, 2, H, G, dv, ns))), dtype=torch.uint8, device=dev)
 
     def win_decode():
         _lib.lm_check(L.ao_lm_window_attention(p(qn), p(kn), p(vn), p(ring_k), p(ring_v), p(first_k), p(first_v), C, 8, 0, p(one), p(last),

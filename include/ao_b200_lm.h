@@ -401,7 +401,7 @@ AO_B200_API int ao_lm_window_attention(const float* qn, const void* kn, const vo
                                        int window, int keep, float scale, float lambda, int unit_rms, float eps, float out_scale,
                                        int n_split, void* workspace, int64_t workspace_bytes, void* out, int64_t ld_out,
                                        void* stream);
-AO_B200_API int64_t ao_lm_window_attention_workspace_bytes(int n_tiles, int n_maps, int G, int dv, int n_split);
+AO_B200_API int64_t ao_lm_window_attention_workspace_bytes(int n_tiles, int n_maps, int H, int G, int dv, int n_split);
 /* The same attention for prompt portions on the tensor cores (bf16 storage; d and dv multiples of 16, dv <= 128): tiles of
  * ao_lm_window_attention_prompt_plan rows (0 = shape not covered), one CTA per (tile, query head). */
 AO_B200_API int ao_lm_window_attention_prompt_plan(int dt, int n_maps, int H, int G, int d, int dv, int* tile_rows);

@@ -344,7 +344,7 @@ def _window_run(q, k, v, cuts, window, keep, scale, lam, ring, first_rows, dtype
         qd = q[a:a + c].float().cuda().contiguous()
         kd, vd = k[a:a + c].cuda().to(tdt).contiguous(), v[a:a + c].cuda().to(tdt).contiguous()
         o = torch.zeros(c, H * dv, device="cuda", dtype=tdt)
-        ws = torch.zeros(max(16, int(L.ao_lm_window_attention_workspace_bytes(len(tf), M, G, dv, n_split))), device="cuda", dtype=torch.uint8)
+        ws = torch.zeros(max(16, int(L.ao_lm_window_attention_workspace_bytes(len(tf), M, H, G, dv, n_split))), device="cuda", dtype=torch.uint8)
         common = (_p(qd), _p(kd), _p(vd), _p(rk), _p(rv), _p(fk), _p(fv), ring, first_rows, dt, _p(sd), _p(pd), _p(bd), _p(tf), _p(tc), len(tf),
                   M, H, G, d, dv, window, keep, scale, lam, unit, eps, out_scale)
         if tensor:
@@ -360,7 +360,7 @@ def _window_run(q, k, v, cuts, window, keep, scale, lam, ring, first_rows, dtype
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,M,d,dv,window,keep", [(4, 2, 2, 8, 12, 9, 2), (3, 1, 2, 5, 7, 4, 0), (2, 2, 1, 16, 40, 13, 5), (6, 2, 2, 24, 33, 1, 1),
-                                                    (1, 1, 2, 64, 128, 20, 30), (16, 1, 2, 8, 8, 6, 1)])
+                                                    (1, 1, 2, 64, 128, 20, 30), (16, 1, 2, 8, 8, 6, 1), (40, 2, 2, 8, 8, 7, 2)])
 def test_window_attention_whole_portions_and_decoding(dtype, H, G, M, d, dv, window, keep):
     T, scale, lam = 61, 0.4, 0.6
     g = _gen(H * 31 + d)

@@ -202,7 +202,7 @@ LM_SIGNATURES = {
     "ao_lm_window_attention_plan": [_i32, _i32, _i32, _i32, _i32, _i32, _p32],
     "ao_lm_window_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                _i32, _i32, _i32, _i32, _i32, _f32, _f32, _i32, _f32, _f32, _i32, _vp, _i64, _vp, _i64, _vp],
-    "ao_lm_window_attention_workspace_bytes": [_i32, _i32, _i32, _i32, _i32],
+    "ao_lm_window_attention_workspace_bytes": [_i32, _i32, _i32, _i32, _i32, _i32],
     "ao_lm_window_attention_prompt_plan": [_i32, _i32, _i32, _i32, _i32, _i32, _p32],
     "ao_lm_window_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                       _i32, _i32, _i32, _i32, _i32, _f32, _f32, _i32, _f32, _f32, _vp, _i64, _vp],

@@ -212,7 +212,7 @@ class StepEngine(SegmentStepEngine):
             _lib.lm_check(L.ao_lm_window_attention_prompt(*common, _p(o), H * dv, st), "window_attention_prompt")
         else:
             ns = self._splits(nt * G, window + keep)    # few rows over a long window: the keys are shared out over more CTAs
-            ws = torch.empty(max(16, int(L.ao_lm_window_attention_workspace_bytes(nt, 2, G, dv, ns))), dtype=torch.uint8, device=dev)
+            ws = torch.empty(max(16, int(L.ao_lm_window_attention_workspace_bytes(nt, 2, H, G, dv, ns))), dtype=torch.uint8, device=dev)
             _lib.lm_check(L.ao_lm_window_attention(*common, ns, _p(ws), ws.numel(), _p(o), H * dv, st), "window_attention")
             c += 1 if ns > 1 else 0
         if self.last_reader[owner] == i:        # nobody reads the old rows any more: the step's rows enter the cache

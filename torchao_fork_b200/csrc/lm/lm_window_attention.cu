@@ -100,7 +100,7 @@ struct WinArgs {
   void* out;                       // [n][ld_out], H * dv per row
   int64_t ld_out;
   int n_split;                     // > 1: blockIdx.z takes a share of the key blocks and leaves (max, denominator, sums) in ws
-  float* ws;                       // [tiles][G][n_split][kPairs][n_maps][dv + 2]
+  float* ws;                       // [tiles][G * head shares][n_split][kPairs][n_maps][dv + 2]
 };
 
 // a_1 - lambda a_2 (or a_1 alone), optionally divided by its root mean square over the head's dv values, times out_scale:
@@ -124,16 +124,19 @@ __device__ __forceinline__ void finish_pair(const WinArgs& a, const float (&av)[
   }
 }
 
-// One CTA = a tile of consecutive rows of one segment x one key/value head; a warp owns up to kSlots (row, query head)
-// pairs and keeps the running maximum, denominator and sums of all their maps in registers.  Key index kk of the tile
+// One CTA = a tile of consecutive rows of one segment x one key/value head (a group of more than kPairs query heads is
+// shared out over several CTAs of one row each); a warp owns up to kSlots (row, query head) pairs and keeps the running
+// maximum, denominator and sums of all their maps in registers.  Key index kk of the tile
 // enumerates the kept first positions that lie in front of the tile's window, then the window from its first row's
 // oldest key to its last row's own position.
 template <typename T, int NM>
 __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, g = blockIdx.y;
-  const int d = a.d, dv = a.dv, rep = a.H / a.G, G = a.G;
+  const int tile = blockIdx.x;
+  const int d = a.d, dv = a.dv, G = a.G;
+  const int rep_all = a.H / G, rep = min(rep_all, kPairs), subs = (rep_all + rep - 1) / rep;
+  const int g = blockIdx.y / subs, h_first = (blockIdx.y % subs) * rep;    // this CTA's query heads of the group: h_first .. + rep
   const int first = a.tile_first[tile], count = a.tile_count[tile];
   const int pa = a.pos[first], back0 = a.back[first];
   const int p0 = pa - back0;                          // the first position the step brings of this sequence
@@ -156,8 +159,8 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
   const T* step_v = static_cast<const T*>(a.vn) + (seg_row0 * G + g) * dv;
 
   for (int i = threadIdx.x; i < npairs * KD; i += blockDim.x) {
-    const int pr = i / KD, c = i - pr * KD, r = pr / rep, qh = g * rep + pr % rep;
-    Qs[i] = a.qn[((int64_t)(first + r) * a.H + qh) * KD + c];
+    const int pr = i / KD, c = i - pr * KD, r = pr / rep, hq = h_first + pr % rep;
+    Qs[i] = hq < rep_all ? a.qn[((int64_t)(first + r) * a.H + g * rep_all + hq) * KD + c] : 0.f;
   }
   float mx[kSlots][NM], den[kSlots][NM], o[kSlots][NM][kMaxDvLane];
 #pragma unroll
@@ -203,7 +206,7 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
 #pragma unroll
     for (int sl = 0; sl < kSlots; ++sl) {
       const int pr = warp + sl * kWarps;
-      if (pr >= npairs) continue;                      // uniform over the warp
+      if (pr >= npairs || h_first + pr % rep >= rep_all) continue;    // uniform over the warp
       const int i_pos = pa + pr / rep;
       if (j_lo > i_pos) continue;                      // the whole block lies in the row's future
       if (k0 >= nf && j_hi <= i_pos - a.window && j_lo >= a.keep) continue;   // ... or behind its window
@@ -255,11 +258,11 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
 #pragma unroll
   for (int sl = 0; sl < kSlots; ++sl) {
     const int pr = warp + sl * kWarps;
-    if (pr >= npairs) continue;
+    if (pr >= npairs || h_first + pr % rep >= rep_all) continue;
     if (a.n_split > 1) {   // this share's maximum, denominator and sums; the merge kernel finishes the pair
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
-        float* w = a.ws + (((((int64_t)tile * G + g) * a.n_split + blockIdx.z) * kPairs + pr) * NM + m) * (dv + 2);
+        float* w = a.ws + (((((int64_t)tile * gridDim.y + blockIdx.y) * a.n_split + blockIdx.z) * kPairs + pr) * NM + m) * (dv + 2);
         if (lane == 0) w[0] = mx[sl][m], w[1] = den[sl][m];
 #pragma unroll
         for (int e = 0; e < kMaxDvLane; ++e)
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
       }
       continue;
     }
-    const int r = pr / rep, qh = g * rep + pr % rep;
+    const int r = pr / rep, qh = g * rep_all + h_first + pr % rep;
     float av[NM][kMaxDvLane];
 #pragma unroll
     for (int m = 0; m < NM; ++m)
@@ -284,17 +287,19 @@ template <typename T, int NM>
 __global__ void __launch_bounds__(kWarps * 32) window_attention_merge_kernel(WinArgs a) {
   extern __shared__ float sm[];    // [kWarps][NM][dv + 2], then [NM][dv]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, g = blockIdx.y, pr = blockIdx.z;
-  const int dv = a.dv, rep = a.H / a.G;
+  const int tile = blockIdx.x, pr = blockIdx.z;
+  const int dv = a.dv;
+  const int rep_all = a.H / a.G, rep = min(rep_all, kPairs), subs = (rep_all + rep - 1) / rep;
+  const int g = blockIdx.y / subs, h_first = (blockIdx.y % subs) * rep;
   const int first = a.tile_first[tile], npairs = a.tile_count[tile] * rep;
-  if (pr >= npairs) return;
+  if (pr >= npairs || h_first + pr % rep >= rep_all) return;
   const int64_t stride = (int64_t)kPairs * NM * (dv + 2);          // from one share to the next
   constexpr int kPer = 64 / kWarps;                                // shares per warp at most
   float* part = sm;
   float* fin = sm + (size_t)kWarps * NM * (dv + 2);
 #pragma unroll
   for (int m = 0; m < NM; ++m) {
-    const float* w0 = a.ws + (((((int64_t)tile * a.G + g) * a.n_split) * kPairs + pr) * NM + m) * (dv + 2);
+    const float* w0 = a.ws + (((((int64_t)tile * gridDim.y + blockIdx.y) * a.n_split) * kPairs + pr) * NM + m) * (dv + 2);
     float mz[kPer], dz[kPer], v[kPer][kMaxDvLane];
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
@@ -347,15 +352,17 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_merge_kernel(Win
     for (int m = 0; m < NM; ++m)
 #pragma unroll
       for (int e = 0; e < kMaxDvLane; ++e) av[m][e] = lane + 32 * e < dv ? fin[m * dv + lane + 32 * e] : 0.f;
-    const int r = pr / rep, qh = g * rep + pr % rep;
+    const int r = pr / rep, qh = g * rep_all + h_first + pr % rep;
     finish_pair<T, NM>(a, av, lane, static_cast<T*>(a.out) + (int64_t)(first + r) * a.ld_out + (int64_t)qh * dv);
   }
 }
 
 inline int win_tile_rows(int H, int G) {
-  if (G <= 0 || H % G || H / G > kPairs) return 0;
-  return kPairs / (H / G);
+  if (G <= 0 || H % G) return 0;
+  return H / G > kPairs ? 1 : kPairs / (H / G);
 }
+// CTAs that share out the query heads of one key/value head
+inline int win_head_shares(int H, int G) { return H / G > kPairs ? (H / G + kPairs - 1) / kPairs : 1; }
 inline size_t win_smem(int nm, int d, int dv) {
   return ((size_t)kPairs * nm * d + (size_t)kKeys * (nm * d + 1) + (size_t)kKeys * dv + (size_t)kWarps * nm * kKeys) * sizeof(float);
 }
@@ -370,10 +377,11 @@ int launch_window(const WinArgs& a, int n_tiles, size_t smem, cudaStream_t st) {
       set = true;
     }
   }
-  kern<<<dim3((unsigned)n_tiles, (unsigned)a.G, (unsigned)a.n_split), kWarps * 32, smem, st>>>(a);
+  const unsigned gy = (unsigned)(a.G * win_head_shares(a.H, a.G));
+  kern<<<dim3((unsigned)n_tiles, gy, (unsigned)a.n_split), kWarps * 32, smem, st>>>(a);
   if (a.n_split > 1) {
     const size_t msm = ((size_t)kWarps * NM * (a.dv + 2) + (size_t)NM * a.dv) * sizeof(float);      // <= 19 KB
-    window_attention_merge_kernel<T, NM><<<dim3((unsigned)n_tiles, (unsigned)a.G, kPairs), kWarps * 32, msm, st>>>(a);
+    window_attention_merge_kernel<T, NM><<<dim3((unsigned)n_tiles, gy, kPairs), kWarps * 32, msm, st>>>(a);
   }
   return lm_launch_status();
 }
@@ -408,8 +416,9 @@ extern "C" int ao_lm_window_append(const void* kn, const void* vn, int64_t n, in
   return lm_launch_status();
 }
 
-extern "C" int64_t ao_lm_window_attention_workspace_bytes(int n_tiles, int n_maps, int G, int dv, int n_split) {
-  return n_split > 1 ? (int64_t)n_tiles * G * n_split * kPairs * n_maps * (dv + 2) * 4 : 0;
+extern "C" int64_t ao_lm_window_attention_workspace_bytes(int n_tiles, int n_maps, int H, int G, int dv, int n_split) {
+  if (n_split <= 1 || G <= 0 || H % G) return 0;
+  return (int64_t)n_tiles * G * win_head_shares(H, G) * n_split * kPairs * n_maps * (dv + 2) * 4;
 }
 
 extern "C" int ao_lm_window_attention_plan(int dt, int n_maps, int H, int G, int d, int dv, int* tile_rows) {
@@ -428,10 +437,10 @@ extern "C" int ao_lm_window_attention(const float* qn, const void* kn, const voi
                                       void* workspace, int64_t workspace_bytes, void* out, int64_t ld_out, void* stream) {
   LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && slot && pos && back && tile_first && tile_count && out);
   LM_CHECK_ARG(n_tiles > 0 && window > 0 && keep >= 0 && ring >= window && first_rows >= keep && (first_rows == 0 || (first_k && first_v)));
-  LM_CHECK_ARG(G > 0 && G <= 65535 && (n_maps == 1 || n_maps == 2) && n_split >= 1 && n_split <= 64);
+  LM_CHECK_ARG(G > 0 && H > 0 && H <= 65535 && (n_maps == 1 || n_maps == 2) && n_split >= 1 && n_split <= 64);
   if (n_split > 1) {
     LM_CHECK_ARG(workspace);
-    if (workspace_bytes < ao_lm_window_attention_workspace_bytes(n_tiles, n_maps, G, dv, n_split)) return AO_B200_ERR_WORKSPACE;
+    if (workspace_bytes < ao_lm_window_attention_workspace_bytes(n_tiles, n_maps, H, G, dv, n_split)) return AO_B200_ERR_WORKSPACE;
   }
   if (win_tile_rows(H, G) == 0 || dv > 32 * kMaxDvLane) return AO_B200_ERR_UNSUPPORTED;
   const size_t smem = win_smem(n_maps, d, dv);
