@@ -240,12 +240,17 @@ def recurrence_and_row_numbers(res, k):
     return res
 
 
-def run(sizes=(("Fedipel-2k", "Rutusun-2k"), ("Fedipel-4k", "Rutusun-4k")), prompt_len=2048, decode_ctx=1536, decode_steps=64):
+def run(sizes=(("Fedipel-2k", "Rutusun-2k"), ("Fedipel-4k", "Rutusun-4k")), expert_sizes=(("Fedipel-2k-moe", "Rutusun-2k-moe"),),
+        prompt_len=2048, decode_ctx=1536, decode_steps=64):
+    """`sizes`: whole models and the kernels alone; `expert_sizes`: whole models whose odd layers are mixtures of experts
+    (the mixers are those of the first size of the same width, so their kernels are not timed again)."""
     out = {"metric": "fedipel_layers_prefill_decode", "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "sizes": {}}
     for name, other in sizes:
         res, k = kernel_numbers(name, prompt_len, decode_ctx)
         out["sizes"][name] = {"models": model_numbers(name, other, prompt_len, decode_ctx, decode_steps),
                               "kernels": recurrence_and_row_numbers(res, k)}
+    for name, other in expert_sizes:
+        out["sizes"][name] = {"models": model_numbers(name, other, prompt_len, decode_ctx, decode_steps)}
     return out
 
 
