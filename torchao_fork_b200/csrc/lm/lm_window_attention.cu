@@ -100,6 +100,7 @@ struct WinArgs {
   void* out;                       // [n][ld_out], H * dv per row
   int64_t ld_out;
   int n_split;                     // > 1: blockIdx.z takes a share of the key blocks and leaves (max, denominator, sums) in ws
+  int vec16;                       // rows of keys and values are whole 16-byte pieces on 16-byte boundaries: staged 16 bytes at a time
   float* ws;                       // [tiles][G * head shares][n_split][kPairs][n_maps][dv + 2]
 };
 
@@ -121,6 +122,35 @@ __device__ __forceinline__ void finish_pair(const WinArgs& a, const float (&av)[
   for (int e = 0; e < kMaxDvLane; ++e) {
     const int c = lane + 32 * e;
     if (c < a.dv) stf(dst + c, val[e] * k);
+  }
+}
+
+// kKeys rows of `width` values (storage type, 16-byte aligned rows, width a multiple of a 16-byte piece) -> fp32 in shared
+// memory, row jj at dst + jj * stride; rows at or past nk become zeros.  A thread's pieces (up to four) are all in flight
+// before the first is stored: a decoded token's CTA otherwise waits for one DRAM round trip per element it fetches.
+template <typename T, typename RowOf>
+__device__ __forceinline__ void stage_key_block(float* dst, int stride, int width, int k0, int nk, RowOf row_of) {
+  constexpr int kPer = 16 / (int)sizeof(T), kFlight = 4;
+  const int per_row = width / kPer, total = kKeys * per_row;
+  for (int base = 0; base < total; base += kFlight * blockDim.x) {
+    uint4 v[kFlight];
+#pragma unroll
+    for (int u = 0; u < kFlight; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (i < total) {
+        const int jj = i / per_row, kk = k0 + jj;
+        if (kk < nk) v[u] = __ldg(reinterpret_cast<const uint4*>(row_of(kk)) + (i - jj * per_row));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kFlight; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      if (i < total) {
+        const int jj = i / per_row;
+        unpack16(v[u], dst + (size_t)jj * stride + (size_t)(i - jj * per_row) * kPer, static_cast<const T*>(nullptr));
+      }
+    }
   }
 }
 
@@ -175,27 +205,40 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(WinArgs a
   const int k_begin = blockIdx.z * per * kKeys, k_end = min(nk, (int)(blockIdx.z + 1) * per * kKeys);
   for (int k0 = k_begin; k0 < k_end; k0 += kKeys) {
     __syncthreads();   // the previous block is used up (and, the first time, the queries are in place)
-    for (int i = threadIdx.x; i < kKeys * KD; i += blockDim.x) {
-      const int jj = i / KD, c = i - jj * KD, kk = k0 + jj;
-      float v = 0.f;
-      if (kk < nk) {
+    if (a.vec16) {
+      stage_key_block<T>(Ks, KP, KD, k0, nk, [&](int kk) {
         const int j = kk < nf ? kk : lo + (kk - nf);
-        const T* src = j >= p0 ? step_k + (int64_t)(j - p0) * G * KD
-                               : (j < a.first_rows ? first_k + (int64_t)j * G * KD : ring_k + (int64_t)(j % a.ring) * G * KD);
-        v = ldf(src + c);
-      }
-      Ks[jj * KP + c] = v;
-    }
-    for (int i = threadIdx.x; i < kKeys * dv; i += blockDim.x) {
-      const int jj = i / dv, c = i - jj * dv, kk = k0 + jj;
-      float v = 0.f;
-      if (kk < nk) {
+        return j >= p0 ? step_k + (int64_t)(j - p0) * G * KD
+                       : (j < a.first_rows ? first_k + (int64_t)j * G * KD : ring_k + (int64_t)(j % a.ring) * G * KD);
+      });
+      stage_key_block<T>(Vs, dv, dv, k0, nk, [&](int kk) {
         const int j = kk < nf ? kk : lo + (kk - nf);
-        const T* src = j >= p0 ? step_v + (int64_t)(j - p0) * G * dv
-                               : (j < a.first_rows ? first_v + (int64_t)j * G * dv : ring_v + (int64_t)(j % a.ring) * G * dv);
-        v = ldf(src + c);
+        return j >= p0 ? step_v + (int64_t)(j - p0) * G * dv
+                       : (j < a.first_rows ? first_v + (int64_t)j * G * dv : ring_v + (int64_t)(j % a.ring) * G * dv);
+      });
+    } else {
+      for (int i = threadIdx.x; i < kKeys * KD; i += blockDim.x) {
+        const int jj = i / KD, c = i - jj * KD, kk = k0 + jj;
+        float v = 0.f;
+        if (kk < nk) {
+          const int j = kk < nf ? kk : lo + (kk - nf);
+          const T* src = j >= p0 ? step_k + (int64_t)(j - p0) * G * KD
+                                 : (j < a.first_rows ? first_k + (int64_t)j * G * KD : ring_k + (int64_t)(j % a.ring) * G * KD);
+          v = ldf(src + c);
+        }
+        Ks[jj * KP + c] = v;
       }
-      Vs[jj * dv + c] = v;
+      for (int i = threadIdx.x; i < kKeys * dv; i += blockDim.x) {
+        const int jj = i / dv, c = i - jj * dv, kk = k0 + jj;
+        float v = 0.f;
+        if (kk < nk) {
+          const int j = kk < nf ? kk : lo + (kk - nf);
+          const T* src = j >= p0 ? step_v + (int64_t)(j - p0) * G * dv
+                                 : (j < a.first_rows ? first_v + (int64_t)j * G * dv : ring_v + (int64_t)(j % a.ring) * G * dv);
+          v = ldf(src + c);
+        }
+        Vs[jj * dv + c] = v;
+      }
     }
     __syncthreads();
     const int kk = k0 + lane;
@@ -445,8 +488,12 @@ extern "C" int ao_lm_window_attention(const float* qn, const void* kn, const voi
   if (win_tile_rows(H, G) == 0 || dv > 32 * kMaxDvLane) return AO_B200_ERR_UNSUPPORTED;
   const size_t smem = win_smem(n_maps, d, dv);
   if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  const int piece = dt == AO_LM_BF16 ? 8 : 4;    // values of the storage type in 16 bytes
+  auto on16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const int vec16 = (n_maps * d) % piece == 0 && dv % piece == 0 && on16(kn) && on16(vn) && on16(ring_k) && on16(ring_v) &&
+                    (!first_k || on16(first_k)) && (!first_v || on16(first_v));
   WinArgs a{qn, kn, vn, ring_k, ring_v, first_k ? first_k : ring_k, first_v ? first_v : ring_v, ring, first_rows, slot, pos, back,
-            tile_first, tile_count, H, G, d, dv, window, keep, scale, lambda, out_scale, eps, unit_rms, out, ld_out, n_split,
+            tile_first, tile_count, H, G, d, dv, window, keep, scale, lambda, out_scale, eps, unit_rms, out, ld_out, n_split, vec16,
             static_cast<float*>(workspace)};
   const cudaStream_t st = lm_stream(stream);
   LM_DISPATCH(dt, {
