@@ -211,7 +211,7 @@ def _decays(heads):
     return [1.0 - 2.0 ** -(3.0 + 6.0 * h / max(1, heads - 1)) for h in range(heads)]
 
 
-def _pattern(n_layer, width, heads, kv_heads, dim, ff, vocab, window=4096, keep=4, experts=0, top=0, expert_ff=0, kinds=None, rank=64):
+def _pattern(n_layer, width, heads, kv_heads, dim, ff, vocab, window=4096, keep=8, experts=0, top=0, expert_ff=0, kinds=None, rank=64):
     """Layers cycling retention -> attention -> wkv; a second attention layer borrows the first one's keys and values;
     feed-forwards alternate dense / mixture (when experts > 0)."""
     kinds = kinds or ("retention", "attention", "wkv")
@@ -219,11 +219,11 @@ def _pattern(n_layer, width, heads, kv_heads, dim, ff, vocab, window=4096, keep=
     for i in range(n_layer):
         kind = kinds[i % len(kinds)]
         if kind == "retention":
-            mixer = RetentionArgs(heads, dim, dim, _decays(heads), RotaryArgs(dim, 1e6))
+            mixer = RetentionArgs(heads, dim, dim, _decays(heads), RotaryArgs(dim, 5e5))
         elif kind == "attention":
             # two maps of dim / 2 per head: the same query / key width per head as one map of `dim`
-            mixer = DiffAttentionArgs(heads, kv_heads, dim // 2, dim, 1.0 / math.sqrt(dim // 2), 0.5, window, keep,
-                                      RotaryArgs(dim // 4, 1e6), first_attn)
+            mixer = DiffAttentionArgs(heads, kv_heads, dim // 2, dim, 1.0 / math.sqrt(dim // 2), 0.6, window, keep,
+                                      RotaryArgs(dim // 4, 1e4), first_attn)
             first_attn = i if first_attn is None else first_attn
         else:
             mixer = WkvArgs(width // 64, 64, rank)
@@ -232,7 +232,7 @@ def _pattern(n_layer, width, heads, kv_heads, dim, ff, vocab, window=4096, keep=
         else:
             mlp = MlpArgs("dense", ff)
         layers.append(LayerArgs(kind, mixer, mlp))
-    return FedipelArgs(vocab, width, 1e-6, 0.7, 30.0, layers)
+    return FedipelArgs(vocab, width, 1e-5, 0.8, 30.0, layers)
 
 
 # named random-init configurations (benchmarks and examples; checkpoints carry their own config.json)
