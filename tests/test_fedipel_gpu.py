@@ -499,16 +499,16 @@ def test_squared_relu_units_tanh_and_soft_cap(dtype):
     t = torch.zeros(n, 50, device="cuda", dtype=dtype)
     lib.lm_check(L.ao_lm_unary_rows(_p(z), F32, n, 50, 1, 0.0, None, 0, _p(t), dt, _st()), "tanh")
     assert _close(t.float(), torch.tanh(z.double()), 1e-6 if dtype == torch.float32 else 1e-2)
-    lib.lm_check(L.ao_lm_unary_rows(_p(z), F32, n, 50, 2, 15.0, None, 0, _p(z), F32, _st()), "softcap")       # in place
-    assert float(z.abs().max()) <= 15.0
+    lib.lm_check(L.ao_lm_unary_rows(_p(z), F32, n, 50, 2, 12.5, None, 0, _p(z), F32, _st()), "softcap")       # in place
+    assert float(z.abs().max()) <= 12.5
 
 
 def test_soft_cap_values():
     lib, L = _lm()
     z = torch.linspace(-80, 80, 331).view(1, -1)
     zd = z.cuda()
-    lib.lm_check(L.ao_lm_unary_rows(_p(zd), F32, 1, z.shape[1], 2, 15.0, None, 0, _p(zd), F32, _st()), "softcap")
-    assert _close(zd, 15.0 * torch.tanh(z.double() / 15.0), 1e-6)
+    lib.lm_check(L.ao_lm_unary_rows(_p(zd), F32, 1, z.shape[1], 2, 12.5, None, 0, _p(zd), F32, _st()), "softcap")
+    assert _close(zd, 12.5 * torch.tanh(z.double() / 12.5), 1e-6)
 
 
 @pytest.mark.parametrize("weight", [False, True])

@@ -1,7 +1,7 @@
 """Tensor-parallel decode on 2 GPUs (NCCL): the int4 TP=2 engine against the TP=1 engine built from the same seed.
 Column-parallel shards and row-parallel shards (split on group boundaries) quantize to exactly the TP=1 integers, so the
 logits differ only by the bf16 rounding of the two partial sums per block: SQNR >= 35 dB, greedy tokens equal.
-Needs 2 GPUs (skipped on the 1-GPU box): run with `gpurun --gpus 2 -- python -m pytest tests/test_tp_gpu.py`."""
+Needs 2 GPUs (skipped where one GPU is visible): `python -m pytest tests/test_tp_gpu.py` on a 2-GPU machine."""
 import os
 import socket
 
